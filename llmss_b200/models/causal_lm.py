@@ -17,6 +17,7 @@ from torch import nn
 
 from ..engine.batch import BatchInput
 from .bedovik import BedovikLM, bedovik_spec, load_bedovik
+from .botalorn import BotalornLM, botalorn_spec, load_botalorn
 from .decoder import DecoderLM
 from .families import FAMILIES
 from .ninelix import NinelixLM, load_ninelix, ninelix_spec
@@ -150,6 +151,20 @@ class NinelixForCausalLM(CausalLM):
         self.core.finalize()
 
 
+class BotalornForCausalLM(CausalLM):
+    """Native architecture (see models/botalorn.py): hyper-connected residual streams, sliding-window attention with
+    shared keys / values, gated delta rule.  Same constructor and forward interface as the HF-shaped classes."""
+    family = "botalorn"
+    float32_on_cuda = True
+
+    def __init__(self, config, weights, fuse_parallel: bool = True):
+        nn.Module.__init__(self)
+        self.config = config
+        self.core = BotalornLM(botalorn_spec(config), weights.process_group, weights.device, weights.dtype)
+        load_botalorn(self.core, weights)
+        self.core.finalize()
+
+
 MODEL_REGISTRY = {
     "gptj": GPTJForCausalLM,
     "gpt_bigcode": GPTBigCodeForCausalLM,
@@ -158,4 +173,5 @@ MODEL_REGISTRY = {
     "llama": LlamaForCausalLM,
     "bedovik": BedovikForCausalLM,
     "ninelix": NinelixForCausalLM,
+    "botalorn": BotalornForCausalLM,
 }

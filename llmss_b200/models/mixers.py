@@ -7,6 +7,11 @@
     q / k / v, per-head query / key norm, a position-dependent query temperature, a learned distance bias and a per-head
     output gate, over the paged cache;
   * ``ParallelPair`` -- two mixers side by side whose normed outputs are averaged;
+  * ``WindowAttention`` -- grouped-query softmax attention over a sliding window with a linear distance penalty per head,
+    query / key norm over the whole projection, a value norm, a factor per query head and a per-head output gate; a
+    layer may attend over the pages another layer writes;
+  * ``DeltaMixer`` -- the gated delta rule (ops.delta_scan) behind short convolutions, with a gated per-head norm;
+  * ``HyperConnection`` -- the read / mix / write weights of one sub-layer over several residual streams;
   * ``DenseFFN``.
 
 Every block says what it keeps per sequence (``state_shapes``), which cache pages it needs (``kv_shape``), and maps
@@ -29,10 +34,12 @@ F32 = torch.float32
 
 
 class LayerCacheView:
-    """What one layer sees of a HybridCache: its own states and pages, under ``prefix`` for nested blocks."""
+    """What one layer sees of a HybridCache: its own states and pages, under ``prefix`` for nested blocks.  ``pages_key``:
+    the layer whose key / value pages this one reads (a layer that shares another layer's keys and values)."""
 
-    def __init__(self, cache, key, prefix: str = ""):
+    def __init__(self, cache, key, prefix: str = "", pages_key=None):
         self.cache, self.key, self.prefix = cache, key, prefix
+        self.pages_key = key if pages_key is None else pages_key
 
     def state(self, name: str):
         return self.cache.state(self.key, self.prefix + name)
@@ -42,11 +49,11 @@ class LayerCacheView:
 
     @property
     def k(self):
-        return self.cache.k(self.key)
+        return self.cache.k(self.pages_key)
 
     @property
     def v(self):
-        return self.cache.v(self.key)
+        return self.cache.v(self.pages_key)
 
 
 class WkvMixer:
@@ -294,6 +301,135 @@ class _PairView(LayerCacheView):
     def __init__(self, lc, prefix, owns_pages):
         super().__init__(lc.cache, lc.key, lc.prefix + prefix)
         self.owns_pages = owns_pages
+
+
+class WindowAttention:
+    """Grouped-query softmax attention without rotation over a sliding window.
+
+        q, k, v = W h  ->  short causal convolution per channel
+        q, k    <- rms_div over the token's WHOLE projection (all heads at once) * weight ;  v_g <- rms_div(v_g) per head
+        score_ij = scale * temp_h * q_i . k_j - slope_h (i - j),  0 <= i - j < window ;  slope_h = 2^(-slope_exp (h + 1) / H)
+        softmax ;  o_h *= sigmoid(W_g h)_h ;  W_o
+    Cached: normed keys and normed values (pages), the last taps - 1 projected rows (state).  ``kv_from`` = key of
+    another layer: this layer has no key / value tensors and attends over that layer's pages with queries of its own (the
+    value norm has no weight, so the lender's normed values are this layer's).  ``window`` None: every earlier token."""
+
+    def __init__(self, width, heads, kv_heads, dim, vdim, taps, scale, window, eps, slope_exp=8.0, kv_from=None):
+        self.width, self.heads, self.kv_heads, self.dim, self.vdim, self.taps = width, heads, kv_heads, dim, vdim, taps
+        self.scale, self.window, self.eps, self.slope_exp, self.kv_from = scale, window, eps, slope_exp, kv_from
+        assert heads % kv_heads == 0, "window attention: query heads must be a multiple of key/value heads"
+        self.own_kv = kv_from is None
+        self.n_conv = heads * dim + ((kv_heads * dim + kv_heads * vdim) if self.own_kv else 0)
+        self.w_in = self.conv_w = self.q_norm = self.k_norm = self.temp = self.slopes = self.w_o = None
+
+    def state_shapes(self):
+        return {"conv": ((self.taps - 1, self.n_conv), F32)} if self.taps > 1 else {}
+
+    def kv_shape(self):
+        return (self.kv_heads, self.dim, self.vdim) if self.own_kv else None
+
+    def weights(self):
+        return [self.w_in, self.conv_w, self.q_norm, self.k_norm, self.temp, self.w_o]
+
+    def set_weights(self, wq, wk, wv, cq, ck, cv, q_norm, k_norm, temp, w_g, w_o):
+        """wk / wv / ck / cv / k_norm are None for a layer that borrows its keys and values."""
+        own = self.own_kv
+        self.w_in = torch.cat([wq, wk, wv, w_g] if own else [wq, w_g], dim=0).contiguous()
+        self.conv_w = torch.cat([cq, ck, cv] if own else [cq], dim=0).contiguous()
+        self.q_norm, self.k_norm, self.temp, self.w_o = q_norm, k_norm, temp, w_o.contiguous()
+        H = self.heads
+        self.slopes = torch.tensor([2.0 ** (-self.slope_exp * (h + 1) / H) for h in range(H)], dtype=F32, device=w_o.device)
+
+    def forward(self, h, batch, lc, dtype):
+        """``lc``: this layer's cache view; its pages (``lc.k`` / ``lc.v``) are the lender's when keys and values are borrowed."""
+        H, G, D, Dv = self.heads, self.kv_heads, self.dim, self.vdim
+        with trace("gemm_in"):
+            y = ops.linear(h, self.w_in, out_dtype=F32)
+        qkv, gate = y[:, :self.n_conv], y[:, self.n_conv:self.n_conv + H]
+        with trace("causal_conv"):
+            qkv = ops.causal_conv(qkv, self.conv_w, None, ACT_NONE, batch, lc.state("conv") if self.taps > 1 else None)
+        own = self.own_kv
+        with trace("qknorm_kv_write"):
+            q = ops.qknorm_kv_write(qkv, H, G if own else 0, D, Dv, self.q_norm, self.k_norm, self.eps, 0.0, 1, batch.positions,
+                                    batch.slot_mapping, lc.k if own else None, lc.v if own else None, out_dtype=dtype,
+                                    norm_whole=True, v_norm=True, q_head_scale=self.temp)
+        with trace("attention_bias"):
+            ctx = ops.attention_bias(q, lc.k, lc.v, batch, H, G, D, Dv, self.scale, None, gate=gate, out_dtype=dtype,
+                                     window=self.window or 0, slopes=self.slopes)
+        with trace("gemm_out"):
+            return ops.linear(ctx, self.w_o, out_dtype=F32)
+
+
+class DeltaMixer:
+    """Gated delta rule with one decay and one write strength per head and token.
+
+        q, k, v = silu(causal_conv(W h)) ;  q, k <- unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q *= dim^(-1/2)
+        beta = sigmoid(W_b h) ;  decay = exp(-exp(A_log_h) softplus(W_a h + dt_bias))
+        S <- decay S ;  u = beta (v - S^T k) ;  S <- S + k u^T ;  o = S^T q
+        out = W_o (rms_div_per_head(o) * norm * silu(W_g h))
+    q / k have ``kv_heads`` heads shared by groups of the ``heads`` value heads.  State per sequence: S (32-bit) and the
+    last taps - 1 projected rows.  One input GEMM over the stacked rows [q | k | v | g | a | b]."""
+
+    UNIT_EPS = 1e-6
+
+    def __init__(self, width, heads, kv_heads, dim, vdim, taps, eps):
+        self.width, self.heads, self.kv_heads, self.dim, self.vdim, self.taps, self.eps = width, heads, kv_heads, dim, vdim, taps, eps
+        assert heads % kv_heads == 0, "delta rule: value heads must be a multiple of query/key heads"
+        self.n_qk, self.n_v = kv_heads * dim, heads * vdim
+        self.n_conv = 2 * self.n_qk + self.n_v
+        self.w_in = self.conv_w = self.dt_bias = self.a_log = self.norm_w = self.w_o = None
+
+    def state_shapes(self):
+        s = {"S": ((self.heads, self.dim, self.vdim), F32)}
+        if self.taps > 1:
+            s["conv"] = ((self.taps - 1, self.n_conv), F32)
+        return s
+
+    def kv_shape(self):
+        return None
+
+    def weights(self):
+        return [self.w_in, self.conv_w, self.dt_bias, self.a_log, self.norm_w, self.w_o]
+
+    def set_weights(self, wq, wk, wv, cq, ck, cv, w_b, w_a, dt_bias, a_log, norm_w, w_g, w_o):
+        self.w_in = torch.cat([wq, wk, wv, w_g, w_a, w_b], dim=0).contiguous()
+        self.conv_w = torch.cat([cq, ck, cv], dim=0).contiguous()
+        self.dt_bias, self.a_log, self.w_o = dt_bias, a_log, w_o.contiguous()
+        self.norm_w = norm_w.repeat(self.heads).contiguous()        # one weight of size vdim shared by the heads
+
+    def forward(self, h, batch, lc, dtype):
+        H, G, D, Dv = self.heads, self.kv_heads, self.dim, self.vdim
+        nc, nv = self.n_conv, self.n_v
+        with trace("gemm_in"):
+            y = ops.linear(h, self.w_in, out_dtype=F32)
+        gate, a_raw, b_raw = y[:, nc:nc + nv], y[:, nc + nv:nc + nv + H], y[:, nc + nv + H:nc + nv + 2 * H]
+        with trace("causal_conv"):
+            qkv = ops.causal_conv(y[:, :nc], self.conv_w, None, ACT_SILU, batch, lc.state("conv") if self.taps > 1 else None)
+        with trace("ssm_dt"):
+            _, log_decay = ops.ssm_dt(a_raw, self.dt_bias, self.a_log)
+        with trace("delta_scan"):
+            o = ops.delta_scan(qkv[:, :self.n_qk], qkv[:, self.n_qk:2 * self.n_qk], qkv[:, 2 * self.n_qk:], log_decay, b_raw, batch,
+                               lc.state("S"), H, G, D, Dv, unit_eps=self.UNIT_EPS, q_scale=D ** -0.5, beta_sigmoid=True)
+        with trace("gated_rmsnorm"):
+            z = ops.gated_rmsnorm(o, gate, GATE_SILU, self.norm_w, H, self.eps, False, out_dtype=dtype)
+        with trace("gemm_out"):
+            return ops.linear(z, self.w_o, out_dtype=F32)
+
+
+class HyperConnection:
+    """Weights of one sub-layer over S residual streams: it reads u = sum_s w_in[s] x_s and writes
+    x_t <- sum_s mix[s, t] x_s + w_out[t] y (ops.hyper_residual).  ``identity(S = 1)`` is the plain residual sum."""
+
+    def __init__(self, w_in, mix, w_out):
+        self.w_in, self.mix, self.w_out = w_in, mix, w_out
+
+    @classmethod
+    def identity(cls, device):
+        one = torch.ones(1, dtype=F32, device=device)
+        return cls(one, one.view(1, 1).clone(), one.clone())
+
+    def weights(self):
+        return [self.w_in, self.mix, self.w_out]
 
 
 class DenseFFN:

@@ -298,20 +298,25 @@ def causal_conv(u, w, bias, act, batch, state):
 
 
 def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions, slot_mapping, k_cache, v_cache,
-                    out_dtype=None):
+                    out_dtype=None, norm_whole=False, v_norm=False, q_head_scale=None):
+    """Query / key norm (per head, or over a token's whole projection), query temperature and per-head factor, optional
+    value norm, append to the pages; hkv = 0 prepares queries only.  See ops.reference.qknorm_kv_write."""
     return _dispatch("qknorm_kv_write", qkv, qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions,
-                     slot_mapping, k_cache, v_cache, out_dtype)
+                     slot_mapping, k_cache, v_cache, out_dtype, norm_whole, v_norm, q_head_scale)
 
 
-def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None):
-    """Causal paged attention with separate key / value sizes, a per-head distance bias table and an output gate.
+def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None,
+                   window=0, slopes=None):
+    """Causal paged attention with separate key / value sizes, a per-head distance bias (a table, and / or a linear
+    penalty ``slopes[h] * distance``), an optional sliding window and an output gate.
     ``bias_over_scale``: dist_bias / scale, kept by the caller for the tensor-core kernels (derived per call if absent)."""
     if _cuda(q):
         from . import cuda_impl as cu
 
-        return cu.attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate, out_dtype, bias_over_scale)
+        return cu.attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate, out_dtype, bias_over_scale,
+                                 window, slopes)
     return ref.attention_bias(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.cu_q, hq, hkv, dk, dv, scale,
-                              dist_bias, gate, out_dtype)
+                              dist_bias, gate, out_dtype, window, slopes)
 
 
 def unary(x, op, out_dtype=None):
@@ -331,6 +336,24 @@ def linear_scan(q, k, v, decay, decay_kind, batch, state, heads, qk_heads, dk, d
 
 def gated_rmsnorm(o, gate, gate_act, weight, groups, eps, gate_first, skip_x=None, skip_d=None, out_dtype=None):
     return _dispatch("gated_rmsnorm", o, o, gate, gate_act, weight, groups, eps, gate_first, skip_x, skip_d, out_dtype)
+
+
+# ----------------------------------------------------------------------------- several residual streams, delta rule
+def embed_sinusoid(tokens, wte, scale, positions, streams=1, base=10000.0):
+    """Scaled token embedding plus the sinusoidal position vector, 32-bit, as ``streams`` equal copies [streams, T, W]."""
+    return _dispatch("embed_sinusoid", wte, tokens, wte, scale, positions, streams, base)
+
+
+def hyper_residual(xs, y=None, mix=None, w_out=None, w_in=None, norm_w=None, eps=0.0, out_dtype=None):
+    """Write a sub-layer's output into the residual streams and / or read the next sub-layer's normed input from them:
+    the counterpart of norm_residual / dyt_residual / postnorm_residual for hyper-connections (in place on ``xs``)."""
+    return _dispatch("hyper_residual", xs, xs, y, mix, w_out, w_in, norm_w, eps, out_dtype)
+
+
+def delta_scan(q, k, v, log_decay, beta, batch, state, heads, qk_heads, dk, dv, unit_eps=None, q_scale=1.0, beta_sigmoid=False):
+    """Gated delta rule (decay, error-correcting write, read-out after the write); see ops.reference.delta_scan."""
+    return _dispatch("delta_scan", v, q, k, v, log_decay, beta, batch, state, heads, qk_heads, dk, dv, unit_eps, q_scale,
+                     beta_sigmoid)
 
 
 def sample(logits, greedy, temperature, top_k, top_p, rng_state, vocab: Optional[int] = None, out=None):

@@ -520,23 +520,40 @@ def causal_conv(u, w, bias, act: int, batch, state):
 
 
 def qknorm_kv_write(qkv, hq: int, hkv: int, dk: int, dv: int, q_w, k_w, eps: float, temp_coef: float, temp_every: int,
-                    positions, slot_mapping, k_cache, v_cache, out_dtype=None):
-    """Per-head RMS norm of queries and keys (one plain weight of size dk each, shared by the heads), the query
-    temperature 1 + coef * ln(floor((p + 1) / every) + 1) at position p (coef = 0: none), and the append of k / v to
-    the paged cache (k_cache [blocks, hkv, bs, dk], v_cache [blocks, hkv, bs, dv]).  qkv [T, hq*dk + hkv*dk + hkv*dv]
-    32-bit.  Returns the queries [T, hq * dk]."""
+                    positions, slot_mapping, k_cache, v_cache, out_dtype=None, norm_whole: bool = False, v_norm: bool = False,
+                    q_head_scale=None):
+    """RMS norm of queries and keys, the query temperature 1 + coef * ln(floor((p + 1) / every) + 1) at position p
+    (coef = 0: none), an optional factor per query head (``q_head_scale`` [hq]), and the append of k / v to the paged
+    cache (k_cache [blocks, hkv, bs, dk], v_cache [blocks, hkv, bs, dv]).  The norm runs per head with one plain weight
+    of size dk shared by the heads, or (``norm_whole``) over all heads of a token at once with a weight of the whole
+    projection's size.  ``v_norm``: every value head is divided by its root mean square (no weight) before it is cached.
+    qkv [T, hq*dk + hkv*dk + hkv*dv] 32-bit; hkv = 0: queries only (a layer that attends over another layer's pages).
+    Returns the queries [T, hq * dk]."""
     T = qkv.shape[0]
-    q = _rms_div(qkv[:, :hq * dk].float().view(T, hq, dk), eps) * q_w.float()
-    k = _rms_div(qkv[:, hq * dk:(hq + hkv) * dk].float().view(T, hkv, dk), eps) * k_w.float()
-    v = qkv[:, (hq + hkv) * dk:].float().view(T, hkv, dv)
+    qf = qkv[:, :hq * dk].float()
+    if norm_whole:
+        q = (_rms_div(qf, eps) * q_w.float()).view(T, hq, dk)
+    else:
+        q = _rms_div(qf.view(T, hq, dk), eps) * q_w.float()
     if temp_coef != 0.0:
         temp = 1.0 + temp_coef * torch.log(torch.div(positions.long() + 1, temp_every, rounding_mode="floor").float() + 1.0)
         q = q * temp[:, None, None]
-    bs = k_cache.shape[2]
-    valid = slot_mapping >= 0
-    slots = slot_mapping[valid].long()
-    k_cache[slots // bs, :, slots % bs, :] = k[valid].to(k_cache.dtype)
-    v_cache[slots // bs, :, slots % bs, :] = v[valid].to(v_cache.dtype)
+    if q_head_scale is not None:
+        q = q * q_head_scale.float()[None, :, None]
+    if hkv > 0:
+        kf = qkv[:, hq * dk:(hq + hkv) * dk].float()
+        if norm_whole:
+            k = (_rms_div(kf, eps) * k_w.float()).view(T, hkv, dk)
+        else:
+            k = _rms_div(kf.view(T, hkv, dk), eps) * k_w.float()
+        v = qkv[:, (hq + hkv) * dk:].float().view(T, hkv, dv)
+        if v_norm:
+            v = _rms_div(v, eps)
+        bs = k_cache.shape[2]
+        valid = slot_mapping >= 0
+        slots = slot_mapping[valid].long()
+        k_cache[slots // bs, :, slots % bs, :] = k[valid].to(k_cache.dtype)
+        v_cache[slots // bs, :, slots % bs, :] = v[valid].to(v_cache.dtype)
     return q.reshape(T, hq * dk).to(out_dtype or k_cache.dtype)
 
 
@@ -558,14 +575,15 @@ def distance_bias_table(rel, max_distance: int):
 
 
 def attention_bias(q, k_cache, v_cache, block_tables, seq_lens, cu_q, hq: int, hkv: int, dk: int, dv: int, scale: float,
-                   dist_bias, gate=None, out_dtype=None):
+                   dist_bias, gate=None, out_dtype=None, window: int = 0, slopes=None):
     """Causal softmax attention over the paged cache with key size dk, value size dv, grouped heads, an additive bias
-    dist_bias[h, min(i - j, last)] per head and distance, and an optional per-head output gate sigmoid(gate[t, h])."""
+    dist_bias[h, min(i - j, last)] per head and distance (or none), a linear penalty slopes[h] * (i - j) taken off the
+    scores (or none), a sliding window (``window`` > 0: query i sees keys j with 0 <= i - j < window), and an optional
+    per-head output gate sigmoid(gate[t, h])."""
     T = q.shape[0]
     bs, g = k_cache.shape[2], hq // hkv
     out = torch.zeros(T, hq, dv, dtype=torch.float32, device=q.device)
     cu, lens = cu_q.tolist(), seq_lens.tolist()
-    last = dist_bias.shape[1] - 1
     for i, L in enumerate(lens):
         q0, q1 = cu[i], cu[i + 1]
         ql = q1 - q0
@@ -579,9 +597,15 @@ def attention_bias(q, k_cache, v_cache, block_tables, seq_lens, cu_q, hq: int, h
         s = torch.matmul(qi, k.transpose(1, 2)) * scale
         qpos = torch.arange(L - ql, L, device=q.device)[:, None]
         kpos = torch.arange(L, device=q.device)[None, :]
-        dist = (qpos - kpos).clamp(min=0, max=last)
-        s = s + dist_bias.float()[:, dist.reshape(-1)].view(hq, ql, L)
-        s = s.masked_fill(kpos > qpos, float("-inf"))
+        if dist_bias is not None:
+            dist = (qpos - kpos).clamp(min=0, max=dist_bias.shape[1] - 1)
+            s = s + dist_bias.float()[:, dist.reshape(-1)].view(hq, ql, L)
+        if slopes is not None:
+            s = s - slopes.float()[:, None, None] * (qpos - kpos).float()[None]
+        hidden = kpos > qpos
+        if window > 0:
+            hidden = hidden | (qpos - kpos >= window)
+        s = s.masked_fill(hidden, float("-inf"))
         out[q0:q1] = torch.matmul(torch.softmax(s, dim=-1), v).permute(1, 0, 2)
     if gate is not None:
         out = out * torch.sigmoid(gate.float())[:, :, None]
@@ -661,3 +685,62 @@ def gated_rmsnorm(o, gate, gate_act: int, weight, groups: int, eps: float, gate_
     if g is not None and not gate_first:
         y = y * g
     return y.to(out_dtype or o.dtype)
+
+
+# ----------------------------------------------------------------------------- several residual streams, delta rule
+def embed_sinusoid(tokens, wte, scale: float, positions, streams: int = 1, base: float = 10000.0):
+    """x[t] = wte[tok_t] * scale + pe(p_t) in 32-bit, pe(p)[c] = sin(p * base^(-2 (c // 2) / W)) for even c and cos of the
+    same angle for odd c (angles in 64-bit).  Returns ``streams`` equal copies, [streams, T, W]."""
+    W = wte.shape[1]
+    c = torch.arange(W, device=wte.device)
+    inv = torch.pow(torch.tensor(base, dtype=torch.float64, device=wte.device), -(2.0 * (c // 2).double()) / W)
+    ang = positions.double()[:, None] * inv[None]
+    pe = torch.where(c % 2 == 0, torch.sin(ang), torch.cos(ang))
+    x = (F.embedding(tokens.long(), wte).float() * scale + pe.float())
+    return x[None].repeat(streams, 1, 1).contiguous()
+
+
+def hyper_residual(xs, y=None, mix=None, w_out=None, w_in=None, norm_w=None, eps: float = 0.0, out_dtype=None):
+    """Residual update and read-out over several streams (hyper-connections), xs [S, T, W] 32-bit, in place:
+         write (``y`` given):   xs_t <- sum_s mix[s, t] xs_s + w_out[t] * y      (all streams from the old ones)
+         read (``w_in`` given): u = sum_s w_in[s] xs_s ;  returns rms_div(u) * norm_w, or u itself without ``norm_w``
+    One stream with mix = [[1]], w_out = w_in = [1] is the plain pre-norm residual sum."""
+    if y is not None:
+        new = torch.einsum("st,sTw->tTw", mix.float(), xs) + w_out.float()[:, None, None] * y.float()[None]
+        xs.copy_(new)
+    if w_in is None:
+        return None
+    u = torch.einsum("s,sTw->Tw", w_in.float(), xs)
+    if norm_w is not None:
+        u = _rms_div(u, eps) * norm_w.float()
+    return u.to(out_dtype or torch.float32)
+
+
+def delta_scan(q, k, v, log_decay, beta, batch, state, heads: int, qk_heads: int, dk: int, dv: int, unit_eps=None,
+               q_scale: float = 1.0, beta_sigmoid: bool = False):
+    """Gated delta rule per head, state S [dk, dv] in 32-bit, in this order per token:
+         S <- exp(log_decay_t) S ;  u = beta_t (v_t - S^T k_t) ;  S <- S + k_t u^T ;  o_t = S^T q_t
+    q, k [T, qk_heads * dk] (head h reads q / k head h // (heads / qk_heads)); ``unit_eps``: q and k are first scaled to
+    x / sqrt(sum(x^2) + unit_eps) per head; q is then multiplied by ``q_scale``.  v [T, heads * dv]; log_decay, beta
+    [T, heads] (``beta_sigmoid``: beta is given before its sigmoid).  ``state`` [slots, heads, dk, dv].  o [T, heads * dv]."""
+    T = v.shape[0]
+    rep = heads // qk_heads
+    qf, kf = q.float().view(T, qk_heads, dk), k.float().view(T, qk_heads, dk)
+    if unit_eps is not None:
+        qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + unit_eps)
+        kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + unit_eps)
+    qf = (qf * q_scale).repeat_interleave(rep, dim=1)
+    kf = kf.repeat_interleave(rep, dim=1)
+    vf = v.float().view(T, heads, dv)
+    a = torch.exp(log_decay.float())
+    b = torch.sigmoid(beta.float()) if beta_sigmoid else beta.float()
+    out = torch.zeros(T, heads, dv, dtype=torch.float32, device=v.device)
+    for q0, q1, ctx, slot in _seq_ranges(batch):
+        S = state[slot].float().clone() if ctx > 0 else torch.zeros(heads, dk, dv, dtype=torch.float32, device=v.device)
+        for t in range(q0, q1):
+            S = S * a[t][:, None, None]
+            u = b[t][:, None] * (vf[t] - torch.einsum("hkv,hk->hv", S, kf[t]))
+            S = S + kf[t][:, :, None] * u[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+        state[slot] = S
+    return out.reshape(T, heads * dv)

@@ -11,7 +11,7 @@ from __future__ import annotations
 import json
 import os
 from pathlib import Path
-from typing import Dict, Iterator, List, Tuple
+from typing import Dict, Iterator, List, Optional, Tuple
 
 import torch
 from safetensors.torch import save_file
@@ -266,6 +266,99 @@ PRESETS.update({
 })
 
 
+def botalorn_config(width: int, vocab: int, layers, streams: Optional[int] = 2, embed_scale: float = 1.0, eps: float = 1e-6) -> dict:
+    """config.json of a Botalorn model.  ``layers``: one dict per layer, {"type": "attention", heads, kv_heads, dim, vdim, conv,
+    optionally window, scale, kv_from} | {"type": "delta", heads, kv_heads, dim, vdim, conv}, each with "mlp": None |
+    {"kind": "dense", "ff"}.  ``streams`` None: one plain residual stream (no hyper-connection tensors)."""
+    out = []
+    for L in layers:
+        m = {k: L[k] for k in ("heads", "kv_heads", "dim", "vdim", "conv")}
+        if L["type"] == "attention":
+            m["scale"] = L.get("scale", L["dim"] ** -0.5)
+            if L.get("window") is not None:
+                m["mask"] = {"size": L["window"]}
+            if L.get("kv_from") is not None:
+                m["kv_from"] = L["kv_from"]
+        f = L.get("mlp")
+        out.append({"type": L["type"], "mixer": m, "mlp": None if f is None else {"kind": "dense", "ff": f["ff"]}})
+    cfg = {"architecture": "Botalorn", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed_scale},
+           "layers": out}
+    if streams is not None:
+        cfg["streams"] = streams
+    return cfg
+
+
+def _botalorn_shapes(cfg: dict):
+    W, V, S = cfg["width"], cfg["vocab"], cfg.get("streams")
+    yield "embed", (V, W), "unit"
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}", L["mixer"]
+        q = f"{p}.mix"
+        yield f"{p}.norm1", (W,), "ln_w"
+        yield f"{p}.shift", (W,), ("u", 0.0, 1.0)
+        subs = ["hc1"] + (["hc2"] if L.get("mlp") is not None else [])
+        if S is not None:
+            for hc in subs:
+                yield f"{p}.{hc}.in", (S,), ("n", 1.0 / S, 0.2)
+                yield f"{p}.{hc}.out", (S,), ("n", 0.7, 0.2)
+                yield f"{p}.{hc}.mix", (S, S), ("hcmix", 0.8, 0.1)
+        nq_att, nk, nv = m["heads"] * m["dim"], m["kv_heads"] * m["dim"], m["kv_heads"] * m["vdim"]
+        if L["type"] == "attention":
+            own = m.get("kv_from") is None
+            for s, n in (("q", nq_att),) + ((("k", nk), ("v", nv)) if own else ()):
+                yield f"{q}.{s}", (n, W), "fan"
+                yield f"{q}.{s}.conv", (n, m["conv"]), ("n", 0.0, m["conv"] ** -0.5)
+            yield f"{q}.q.norm", (nq_att,), "ln_w"
+            if own:
+                yield f"{q}.k.norm", (nk,), "ln_w"
+            yield f"{q}.temp", (m["heads"],), ("n", 1.0, 0.2)
+            yield f"{q}.g", (m["heads"], W), "fan"
+            yield f"{q}.o", (W, m["heads"] * m["vdim"]), "fan"
+        else:
+            inner = m["heads"] * m["vdim"]
+            for s, n in (("q", nk), ("k", nk), ("v", inner)):
+                yield f"{q}.{s}", (n, W), "fan"
+                yield f"{q}.{s}.conv", (n, m["conv"]), ("n", 0.0, m["conv"] ** -0.5)
+            yield f"{q}.b", (m["heads"], W), "fan"
+            yield f"{q}.a", (m["heads"], W), "fan"
+            yield f"{q}.dt_bias", (m["heads"],), ("n", -1.0, 1.0)
+            yield f"{q}.A_log", (m["heads"],), ("n", -1.0, 0.7)
+            yield f"{q}.norm", (m["vdim"],), "ln_w"
+            yield f"{q}.g", (inner, W), "fan"
+            yield f"{q}.o", (W, inner), "fan"
+        if L.get("mlp") is not None:
+            yield f"{p}.norm2", (W,), "ln_w"
+            yield f"{p}.mlp.up", (L["mlp"]["ff"], W), "fan"
+            yield f"{p}.mlp.down", (W, L["mlp"]["ff"]), "fan"
+    yield "final.norm", (W,), "ln_w"
+    yield "head", (V, W), "fan"
+
+
+def _botalorn_preset(width, vocab, heads, ff, n_blocks, window=512, kv_div=4):
+    """``n_blocks`` x (attention, attention, delta, delta, attention <- keys / values of the block's second layer, delta), every layer
+    with a dense feed-forward; head size 128."""
+    d = 128
+    att = dict(type="attention", heads=heads, kv_heads=max(1, heads // kv_div), dim=d, vdim=d, conv=4, window=window, mlp={"ff": ff})
+    dlt = dict(type="delta", heads=heads, kv_heads=max(1, heads // 2), dim=d, vdim=d, conv=4, mlp={"ff": ff})
+    layers = []
+    for b in range(n_blocks):
+        base = 6 * b
+        layers += [dict(att), dict(att), dict(dlt), dict(dlt), dict(att, kv_from=base + 1), dict(dlt)]
+    return botalorn_config(width, vocab, layers, streams=2, embed_scale=width ** 0.5)
+
+
+PRESETS.update({
+    "botalorn-tiny": botalorn_config(128, 320, [
+        dict(type="attention", heads=4, kv_heads=2, dim=24, vdim=16, conv=3, window=20, mlp={"ff": 192}),
+        dict(type="delta", heads=4, kv_heads=2, dim=24, vdim=16, conv=4, mlp={"ff": 192}),
+        dict(type="attention", heads=4, kv_heads=2, dim=24, vdim=16, conv=2, window=33, kv_from=0, mlp=None),
+        dict(type="delta", heads=2, kv_heads=2, dim=32, vdim=40, conv=3, mlp={"ff": 160})], streams=3, embed_scale=8.0),
+    # sizes whose layers resemble a served model's (random weights), beside gptj-like-* of equal width and depth
+    "botalorn-2k": _botalorn_preset(2048, 32000, 16, 4096, 3),
+    "botalorn-4k": _botalorn_preset(4096, 32000, 32, 6144, 3),
+})
+
+
 def _shapes(cfg: dict) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
     """(name, shape, kind) for every tensor of the family; kind in {w, b, ln_w, ln_b, emb} (and, for architectures whose
     activations must keep unit scale without trained weights: unit, fan, fan2, alpha, ls)."""
@@ -274,6 +367,8 @@ def _shapes(cfg: dict) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
         yield from _bedovik_shapes(cfg)
     elif mt == "ninelix":
         yield from _ninelix_shapes(cfg)
+    elif mt == "botalorn":
+        yield from _botalorn_shapes(cfg)
     elif mt == "gptj":
         H, L, V = cfg["n_embd"], cfg["n_layer"], cfg["vocab_size"]
         F = cfg.get("n_inner") or 4 * H
@@ -415,9 +510,12 @@ def write_random_checkpoint(path, preset_or_cfg, dtype=torch.float16, device=Non
             shard, size = {}, 0
 
     for name, shape, kind in _shapes(cfg):
-        if isinstance(kind, tuple):      # ("n", mean, std): normal; ("u", lo, hi): uniform
-            r = (torch.randn if kind[0] == "n" else torch.rand)(shape, generator=gen, device=device, dtype=torch.float32)
-            t = kind[1] + kind[2] * r if kind[0] == "n" else kind[1] + (kind[2] - kind[1]) * r
+        if isinstance(kind, tuple):      # ("n", mean, std): normal; ("u", lo, hi): uniform; ("hcmix", diagonal, std): near a scaled identity
+            r = (torch.rand if kind[0] == "u" else torch.randn)(shape, generator=gen, device=device, dtype=torch.float32)
+            if kind[0] == "hcmix":
+                t = kind[1] * torch.eye(shape[0], device=device) + kind[2] * r
+            else:
+                t = kind[1] + kind[2] * r if kind[0] == "n" else kind[1] + (kind[2] - kind[1]) * r
         elif kind in ("unit", "fan", "fan2", "alpha", "ls"):
             r = torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
             t = {"unit": r, "fan": r * shape[-1] ** -0.5 if shape else r, "fan2": 2.0 * r * shape[-1] ** -0.5 if shape else r,
