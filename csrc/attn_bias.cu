@@ -9,6 +9,11 @@
 //                     its warps share every 32-key tile of K and V, staged once in shared memory in 32-bit.  A warp owns
 //                     one pair: lane = key inside the tile for the scores, lane = output channel (mod 32) for P V.
 //                     Scores, softmax and accumulation are 32-bit with full-precision exponentials.
+//                     Optional: a linear penalty slopes[h] * (i - j) taken off the scores, and a sliding window (keys with
+//                     i - j >= window are hidden; the key loop starts at the first row's window).
+//   qkv_prepare     : the general form of qknorm_kv_write, one CTA per token: query / key norm per head or over the token's
+//                     whole projection, a factor per query head, values divided by their per-head root mean square, queries
+//                     only (no keys / values) for a layer that attends over another layer's pages.
 // Page layouts: keys [num_blocks, kv_heads, block_size, dk], values [num_blocks, kv_heads, block_size, dv].
 #include "common.cuh"
 
@@ -60,12 +65,72 @@ __global__ void __launch_bounds__(256) head_gate_kernel(T* __restrict__ x, int64
   }
 }
 
+// One CTA per token.  Pass 1: the sum of squares of every head (queries, keys, values), a warp per head; pass 2: the norms
+// (a head's own sum, or the sum over all query / all key heads of the token) and the writes.  whole = 1: q_w / k_w have the
+// size of the whole projection; else one weight of size dk shared by the heads.
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restrict__ qkv, int64_t ld, int hq, int hkv, int dk, int dv,
+                                                          const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                                          float coef, int every, const float* __restrict__ q_head_scale, int whole,
+                                                          int v_norm, const int* __restrict__ positions, const int* __restrict__ slots,
+                                                          T* __restrict__ k_cache, T* __restrict__ v_cache, int bs, T* __restrict__ q_out) {
+  extern __shared__ float hsum[];     // [hq + 2 hkv] sums of squares, then [2] the whole-projection factors
+  const int64_t t = blockIdx.x;
+  const int nh = hq + 2 * hkv, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* row = qkv + t * ld;
+  const int slot = hkv > 0 ? slots[t] : -1;
+  for (int h = warp; h < nh; h += nw) {
+    const bool isv = h >= hq + hkv;
+    const float* x = isv ? row + (int64_t)(hq + hkv) * dk + (int64_t)(h - hq - hkv) * dv : row + (int64_t)h * dk;
+    const int n = isv ? dv : dk;
+    float ss = 0.f;
+    for (int c = lane; c < n; c += 32) ss = fmaf(x[c], x[c], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) hsum[h] = ss;
+  }
+  __syncthreads();
+  if (whole && threadIdx.x < 2) {
+    const int lo = threadIdx.x == 0 ? 0 : hq, n = threadIdx.x == 0 ? hq : hkv;
+    float tot = 0.f;
+    for (int h = 0; h < n; ++h) tot += hsum[lo + h];
+    hsum[nh + threadIdx.x] = n > 0 ? rsqrtf(tot / ((float)n * dk) + eps) : 0.f;
+  }
+  __syncthreads();
+  float temp = 1.f;
+  if (coef != 0.f) temp = 1.f + coef * logf((float)((positions[t] + 1) / every) + 1.f);
+  for (int h = warp; h < nh; h += nw) {
+    if (h < hq) {
+      float r = whole ? hsum[nh] : rsqrtf(hsum[h] / dk + eps);
+      r *= temp;
+      if (q_head_scale != nullptr) r *= q_head_scale[h];
+      const float* x = row + (int64_t)h * dk;
+      const float* w = q_w + (whole ? (int64_t)h * dk : 0);
+      for (int c = lane; c < dk; c += 32) q_out[t * hq * dk + (int64_t)h * dk + c] = from_f32<T>(x[c] * r * w[c]);
+    } else if (slot >= 0 && h < hq + hkv) {
+      const int g = h - hq;
+      const float r = whole ? hsum[nh + 1] : rsqrtf(hsum[h] / dk + eps);
+      const float* x = row + (int64_t)h * dk;
+      const float* w = k_w + (whole ? (int64_t)g * dk : 0);
+      T* dst = k_cache + (((int64_t)(slot / bs) * hkv + g) * bs + slot % bs) * dk;
+      for (int c = lane; c < dk; c += 32) dst[c] = from_f32<T>(x[c] * r * w[c]);
+    } else if (slot >= 0) {
+      const int g = h - hq - hkv;
+      const float r = v_norm ? rsqrtf(hsum[h] / dv + eps) : 1.f;
+      const float* x = row + (int64_t)(hq + hkv) * dk + (int64_t)g * dv;
+      T* dst = v_cache + (((int64_t)(slot / bs) * hkv + g) * bs + slot % bs) * dv;
+      for (int c = lane; c < dv; c += 32) dst[c] = from_f32<T>(x[c] * r);
+    }
+  }
+}
+
 struct AbArgs {
   const void* q; int64_t ldq;
   const void* k_cache; const void* v_cache;
   const int* block_tables; int max_blocks, bs;
   const int* seq_lens; const int* cu_q;
   const float* bias; int n_dist;          // [hq][n_dist]
+  const float* slopes;                    // [hq] linear distance penalty, or null
+  int window;                             // > 0: only keys with i - j < window are visible
   const float* gate; int64_t ldg;         // [T][hq] logits, or null
   void* out;                              // [T][hq * dv]
   int hq, hkv, dk, dv, nh, rows, hsub;    // nh: query heads per CTA; rows: query rows per CTA; hsub: CTAs per kv head
@@ -105,7 +170,10 @@ __global__ void __launch_bounds__(NW * 32) attention_bias_kernel(AbArgs a) {
   const T* kc = reinterpret_cast<const T*>(a.k_cache);
   const T* vc = reinterpret_cast<const T*>(a.v_cache);
   const float* brow = a.bias != nullptr ? a.bias + (int64_t)(active ? h : 0) * a.n_dist : nullptr;
-  for (int k0 = 0; k0 < kend; k0 += TK) {
+  const float slope = a.slopes != nullptr && active ? a.slopes[h] : 0.f;
+  const int kbeg = a.window > 0 ? max(0, ctx + r0 - a.window + 1) : 0;      // first key any row of this CTA sees
+  const int klo = a.window > 0 ? qpos - a.window + 1 : 0;                   // first key this warp's row sees
+  for (int k0 = kbeg; k0 < kend; k0 += TK) {
     const int nk = min(TK, kend - k0);
     __syncthreads();
     for (int idx = threadIdx.x; idx < nk * dk; idx += NW * 32) {
@@ -119,18 +187,20 @@ __global__ void __launch_bounds__(NW * 32) attention_bias_kernel(AbArgs a) {
       vs[kk * dv + c] = to_f32(vc[(((int64_t)blk * a.hkv + g) * a.bs + pos % a.bs) * dv + c]);
     }
     __syncthreads();
-    if (!active || k0 > qpos) continue;
+    if (!active || k0 > qpos || k0 + nk <= klo) continue;
     const int kpos = k0 + lane;
     float sc = -INFINITY;
-    if (lane < nk && kpos <= qpos) {
+    if (lane < nk && kpos <= qpos && kpos >= klo) {
       float d = 0.f;
       const float* kr = ks + lane * dkp;
       const float* qr = qs + warp * dk;
       for (int c = 0; c < dk; ++c) d = fmaf(qr[c], kr[c], d);
       sc = d;
       if (brow != nullptr) sc += brow[min(qpos - kpos, a.n_dist - 1)];
+      sc -= slope * (float)(qpos - kpos);
     }
     const float mt = warp_max(sc);
+    if (mt == -INFINITY) continue;               // nothing of this tile is visible to the row (warp-uniform)
     const float mn = fmaxf(m, mt);
     const float corr = expf(m - mn);            // m = -inf on the first tile: 0
     const float p = sc == -INFINITY ? 0.f : expf(sc - mn);
@@ -175,6 +245,27 @@ LLMSS_API int llmss_qknorm_kv_write(const float* qkv, int64_t ld, int hq, int hk
   return 0;
 }
 
+// General form of llmss_qknorm_kv_write: norm per head (whole = 0, weights [dk]) or over the token's whole q / k projection
+// (whole = 1, weights [hq * dk] / [hkv * dk]); q_head_scale [hq] or null; v_norm = 1: values / their per-head rms; hkv = 0:
+// queries only (k_cache / v_cache / slots unused).
+LLMSS_API int llmss_qkv_prepare(const float* qkv, int64_t ld, int hq, int hkv, int dk, int dv, const float* q_w, const float* k_w,
+                                float eps, float temp_coef, int temp_every, const float* q_head_scale, int whole, int v_norm,
+                                const int* positions, const int* slots, void* k_cache, void* v_cache, int block_size, void* q_out,
+                                int T_, int dtype, cudaStream_t stream) {
+  LLMSS_REQUIRE(hq > 0 && hkv >= 0 && temp_every > 0, "qkv_prepare: bad sizes");
+  LLMSS_REQUIRE(hkv == 0 || (k_cache != nullptr && v_cache != nullptr && slots != nullptr && k_w != nullptr), "qkv_prepare: keys without pages");
+  if (T_ <= 0) return 0;
+  const size_t smem = sizeof(float) * (size_t)(hq + 2 * hkv + 2);
+  LLMSS_REQUIRE(smem <= 48 * 1024, "qkv_prepare: too many heads");
+  const int nh = hq + 2 * hkv;
+  const int threads = nh >= 8 ? 256 : (nh >= 4 ? 128 : 64);
+  LLMSS_BY_DTYPE(dtype, (qkv_prepare_kernel<T><<<T_, threads, smem, stream>>>(qkv, ld, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every,
+                                                                             q_head_scale, whole, v_norm, positions, slots, (T*)k_cache,
+                                                                             (T*)v_cache, block_size, (T*)q_out)));
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 LLMSS_API int llmss_head_gate(void* x, int64_t ldx, const float* gate, int64_t ldg, int T_, int hq, int dv, int dtype,
                               cudaStream_t stream) {
   if (T_ <= 0) return 0;
@@ -183,17 +274,17 @@ LLMSS_API int llmss_head_gate(void* x, int64_t ldx, const float* gate, int64_t l
   return 0;
 }
 
-LLMSS_API int llmss_attention_bias(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
-                                   int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias,
-                                   int n_dist, const float* gate, int64_t ldg, void* out, int B, int max_q, int hq, int hkv, int dk,
-                                   int dv, float scale, int dtype, cudaStream_t stream) {
+static int attention_bias_launch(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                                 int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias,
+                                 int n_dist, const float* slopes, int window, const float* gate, int64_t ldg, void* out, int B,
+                                 int max_q, int hq, int hkv, int dk, int dv, float scale, int dtype, cudaStream_t stream) {
   LLMSS_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_bias: %d query heads over %d key/value heads", hq, hkv);
   LLMSS_REQUIRE(dv <= 32 * MAXV, "attention_bias: value size %d (at most %d)", dv, 32 * MAXV);
   LLMSS_REQUIRE(bias == nullptr || n_dist > 0, "attention_bias: empty bias table");
   if (B <= 0 || max_q <= 0) return 0;
   AbArgs a;
   a.q = q; a.ldq = ldq; a.k_cache = k_cache; a.v_cache = v_cache; a.block_tables = block_tables; a.max_blocks = max_blocks;
-  a.bs = block_size; a.seq_lens = seq_lens; a.cu_q = cu_q; a.bias = bias; a.n_dist = n_dist; a.gate = gate; a.ldg = ldg; a.out = out;
+  a.bs = block_size; a.seq_lens = seq_lens; a.cu_q = cu_q; a.bias = bias; a.n_dist = n_dist; a.slopes = slopes; a.window = window; a.gate = gate; a.ldg = ldg; a.out = out;
   a.hq = hq; a.hkv = hkv; a.dk = dk; a.dv = dv; a.scale = scale;
   const int gsz = hq / hkv;
   a.nh = gsz < NW ? gsz : NW;
@@ -216,4 +307,22 @@ LLMSS_API int llmss_attention_bias(const void* q, int64_t ldq, const void* k_cac
 #undef LLMSS_AB
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+LLMSS_API int llmss_attention_bias(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                                   int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias,
+                                   int n_dist, const float* gate, int64_t ldg, void* out, int B, int max_q, int hq, int hkv, int dk,
+                                   int dv, float scale, int dtype, cudaStream_t stream) {
+  return attention_bias_launch(q, ldq, k_cache, v_cache, block_tables, max_blocks, block_size, seq_lens, cu_q, bias, n_dist, nullptr, 0,
+                               gate, ldg, out, B, max_q, hq, hkv, dk, dv, scale, dtype, stream);
+}
+
+// the same with a linear distance penalty per head (slopes [hq] or null) and a sliding window (window > 0)
+LLMSS_API int llmss_attention_window(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                                     int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias,
+                                     int n_dist, const float* slopes, int window, const float* gate, int64_t ldg, void* out, int B,
+                                     int max_q, int hq, int hkv, int dk, int dv, float scale, int dtype, cudaStream_t stream) {
+  LLMSS_REQUIRE(window >= 0, "attention_window: window %d", window);
+  return attention_bias_launch(q, ldq, k_cache, v_cache, block_tables, max_blocks, block_size, seq_lens, cu_q, bias, n_dist, slopes,
+                               window, gate, ldg, out, B, max_q, hq, hkv, dk, dv, scale, dtype, stream);
 }

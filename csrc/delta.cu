@@ -1,0 +1,165 @@
+// Gated delta rule over a packed batch (same batch convention as recurrent.cu: cu_q / seq_lens / state slots).
+//
+//   per head and token:  S <- g_t S ;  u = beta_t (v_t - S^T k_t) ;  S <- S + k_t u^T ;  o_t = S^T q_t
+//
+// Every value column of the state is a recurrence of its own (S^T k, the write and the read-out only couple the rows of one
+// column), so thread (j, r) keeps rows [r * KPT, r * KPT + KPT) of column j in registers and the R threads of a column meet
+// in two warp-shuffle sums per token.  One block = one (sequence, head, slice of value columns); the block that reads a
+// slot's old state is the block that writes its new one.  Tokens are staged 16 at a time through shared memory: q and k in
+// strips of KPT + 4 floats (the strips a warp reads together lie in different banks, every read a 16-byte one; strips beyond
+// dk hold zeros), made unit vectors there (x / sqrt(sum x^2 + eps), q times its scale), decays exp(log g) and write
+// strengths (sigmoid taken here if asked) beside them.  The state lies in memory column-major per head ([dv][dk]).
+// Everything is 32-bit with full-precision exponentials.
+#include "common.cuh"
+
+namespace {
+
+constexpr int DTCH = 16;
+
+struct DeltaArgs {
+  const float* q; int64_t ldq;
+  const float* k; int64_t ldk;
+  const float* v; int64_t ldv;
+  const float* log_decay; int64_t ldg;   // [T, H]
+  const float* beta; int64_t ldb;        // [T, H]
+  float* out;                            // [T, H * dv]
+  float* state;                          // [slots, H, dv, dk]
+  const int* cu_q; const int* seq_lens; const int* slots;
+  int H, rep, dk, dv, dvt, R;
+  float unit_eps, q_scale;
+  int unit, beta_sigmoid;
+};
+
+template <int KPT>
+__global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
+  constexpr int STRIP = KPT + 4;
+  extern __shared__ __align__(16) float sm[];
+  const int b = blockIdx.x;
+  const int q0 = a.cu_q[b], ql = a.cu_q[b + 1] - q0, ctx = a.seq_lens[b] - ql, slot = a.slots[b];
+  if (slot < 0 || ctx < 0 || ql <= 0) return;
+  const int h = blockIdx.y, hk = h / a.rep;
+  const int j0 = blockIdx.z * a.dvt, nj = min(a.dvt, a.dv - j0);
+  const int dk = a.dk, R = a.R, row = R * STRIP, nthr = blockDim.x;
+  const int jl = threadIdx.x / R, r = threadIdx.x % R;
+  const bool live = jl < nj;
+  const int j = j0 + jl, i0 = r * KPT;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = nthr >> 5;
+  float* qs = sm;                    // [DTCH][row]
+  float* ks = qs + DTCH * row;       // [DTCH][row]
+  float* vs = ks + DTCH * row;       // [DTCH][dvt]
+  float* gs = vs + DTCH * a.dvt;     // [DTCH] decays
+  float* bs = gs + DTCH;             // [DTCH] write strengths
+  float S[KPT];
+  float* sp = a.state + (((int64_t)slot * a.H + h) * a.dv + (live ? j : 0)) * dk;
+#pragma unroll
+  for (int ii = 0; ii < KPT; ++ii) S[ii] = (live && ctx > 0 && i0 + ii < dk) ? sp[i0 + ii] : 0.f;
+  for (int t0 = 0; t0 < ql; t0 += DTCH) {
+    const int nt = min(DTCH, ql - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * row; idx += nthr) {
+      const int tt = idx / row, w = idx % row, ii = w % STRIP, c = (w / STRIP) * KPT + ii;
+      const bool ok = ii < KPT && c < dk;
+      const int64_t t = q0 + t0 + tt;
+      qs[idx] = ok ? a.q[t * a.ldq + (int64_t)hk * dk + c] : 0.f;
+      ks[idx] = ok ? a.k[t * a.ldk + (int64_t)hk * dk + c] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < nt * a.dvt; idx += nthr) {
+      const int tt = idx / a.dvt, c = idx % a.dvt;
+      vs[idx] = c < nj ? a.v[(int64_t)(q0 + t0 + tt) * a.ldv + (int64_t)h * a.dv + j0 + c] : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      const int64_t t = q0 + t0 + threadIdx.x;
+      gs[threadIdx.x] = expf(a.log_decay[t * a.ldg + h]);
+      const float bb = a.beta[t * a.ldb + h];
+      bs[threadIdx.x] = a.beta_sigmoid ? 1.f / (1.f + expf(-bb)) : bb;
+    }
+    __syncthreads();
+    if (a.unit || a.q_scale != 1.f) {
+      for (int tt = warp; tt < nt; tt += nwarp) {
+        float sq = 0.f, sk = 0.f;
+        for (int w = lane; w < row; w += 32) {
+          sq = fmaf(qs[tt * row + w], qs[tt * row + w], sq);
+          sk = fmaf(ks[tt * row + w], ks[tt * row + w], sk);
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        const float rq = (a.unit ? rsqrtf(sq + a.unit_eps) : 1.f) * a.q_scale, rk = a.unit ? rsqrtf(sk + a.unit_eps) : 1.f;
+        for (int w = lane; w < row; w += 32) {
+          qs[tt * row + w] *= rq;
+          ks[tt * row + w] *= rk;
+        }
+      }
+      __syncthreads();
+    }
+    for (int tt = 0; tt < nt; ++tt) {
+      const float g = gs[tt], be = bs[tt];
+      const float* kr = ks + tt * row + r * STRIP;
+      const float* qr = qs + tt * row + r * STRIP;
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < KPT; ii += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + ii);
+        d0 = fmaf(S[ii], k4.x, d0); d1 = fmaf(S[ii + 1], k4.y, d1); d2 = fmaf(S[ii + 2], k4.z, d2); d3 = fmaf(S[ii + 3], k4.w, d3);
+      }
+      float d = (d0 + d1) + (d2 + d3);
+      for (int o = R >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      const float u = be * (vs[tt * a.dvt + jl] - g * d);
+      float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < KPT; ii += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + ii);
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + ii);
+        S[ii] = fmaf(g, S[ii], k4.x * u); S[ii + 1] = fmaf(g, S[ii + 1], k4.y * u);
+        S[ii + 2] = fmaf(g, S[ii + 2], k4.z * u); S[ii + 3] = fmaf(g, S[ii + 3], k4.w * u);
+        e0 = fmaf(S[ii], q4.x, e0); e1 = fmaf(S[ii + 1], q4.y, e1); e2 = fmaf(S[ii + 2], q4.z, e2); e3 = fmaf(S[ii + 3], q4.w, e3);
+      }
+      float o = (e0 + e1) + (e2 + e3);
+      for (int s = R >> 1; s > 0; s >>= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
+      if (live && r == 0) a.out[(int64_t)(q0 + t0 + tt) * a.H * a.dv + (int64_t)h * a.dv + j] = o;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int ii = 0; ii < KPT; ++ii) if (i0 + ii < dk) sp[i0 + ii] = S[ii];
+  }
+}
+
+}  // namespace
+
+// q, k [T, qk_heads * dk] (value head h reads q / k head h / (heads / qk_heads)); v [T, heads * dv]; log_decay, beta [T, heads];
+// out [T, heads * dv]; state [slots, heads, dv, dk].  unit_eps >= 0: q and k become x / sqrt(sum x^2 + unit_eps) per head first.
+LLMSS_API int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
+                               const float* log_decay, int64_t ldg, const float* beta, int64_t ldb, float* out, float* state,
+                               const int* cu_q, const int* seq_lens, const int* slots, int B, int heads, int qk_heads, int dk, int dv,
+                               float unit_eps, float q_scale, int beta_sigmoid, cudaStream_t stream) {
+  LLMSS_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0, "delta_scan: %d value heads over %d query/key heads", heads, qk_heads);
+  LLMSS_REQUIRE(dk > 0 && dk <= 1024 && dv > 0, "delta_scan: key size %d (at most 1024), value size %d", dk, dv);
+  if (B <= 0) return 0;
+  DeltaArgs a;
+  a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.log_decay = log_decay; a.ldg = ldg; a.beta = beta; a.ldb = ldb;
+  a.out = out; a.state = state; a.cu_q = cu_q; a.seq_lens = seq_lens; a.slots = slots;
+  a.H = heads; a.rep = heads / qk_heads; a.dk = dk; a.dv = dv;
+  a.unit = unit_eps >= 0.f ? 1 : 0; a.unit_eps = unit_eps >= 0.f ? unit_eps : 0.f; a.q_scale = q_scale; a.beta_sigmoid = beta_sigmoid;
+  const int kpt = dk <= 8 ? 8 : (dk <= 16 ? 16 : 32);
+  int R = 1;
+  while (R * kpt < dk) R *= 2;
+  a.R = R;
+  int threads = ((dv * R + 31) / 32) * 32;
+  threads = threads > 256 ? 256 : threads;
+  a.dvt = threads / R;
+  const dim3 grid(B, heads, (dv + a.dvt - 1) / a.dvt);
+  LLMSS_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "delta_scan: grid too large");
+  const size_t smem = sizeof(float) * ((size_t)2 * DTCH * R * (kpt + 4) + (size_t)DTCH * a.dvt + 2 * DTCH);
+#define LLMSS_DS(K)                                                                     \
+  do {                                                                                  \
+    static PerDeviceSmem gsm;                                                           \
+    if (smem > 48 * 1024) LLMSS_CHECK_CUDA(gsm.ensure(delta_scan_kernel<K>, (int)smem)); \
+    delta_scan_kernel<K><<<grid, threads, smem, stream>>>(a);                           \
+  } while (0)
+  if (kpt == 8) LLMSS_DS(8);
+  else if (kpt == 16) LLMSS_DS(16);
+  else LLMSS_DS(32);
+#undef LLMSS_DS
+  LLMSS_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -314,6 +314,33 @@ int llmss_attention_bias(const void* q, int64_t ldq, const void* k_cache, const 
                          const float* gate, int64_t ldg, void* out, int B, int max_q, int hq, int hkv, int dk, int dv, float scale,
                          int dtype, llmss_stream_t stream);
 
+/* General query / key / value preparation: norm per head (whole = 0) or over a token's whole projection (whole = 1, weights of
+ * that size), a factor per query head, values divided by their per-head rms (v_norm), hkv = 0 for queries only. */
+int llmss_qkv_prepare(const float* qkv, int64_t ld, int hq, int hkv, int dk, int dv, const float* q_w, const float* k_w, float eps,
+                      float temp_coef, int temp_every, const float* q_head_scale, int whole, int v_norm, const int* positions,
+                      const int* slots, void* k_cache, void* v_cache, int block_size, void* q_out, int T, int dtype,
+                      llmss_stream_t stream);
+/* llmss_attention_bias with a linear penalty slopes[h] * distance (or null) and a sliding window (window > 0: distance < window) */
+int llmss_attention_window(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                           int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias, int n_dist,
+                           const float* slopes, int window, const float* gate, int64_t ldg, void* out, int B, int max_q, int hq,
+                           int hkv, int dk, int dv, float scale, int dtype, llmss_stream_t stream);
+
+/* ---- several residual streams and the gated delta rule (csrc/streams.cu, csrc/delta.cu) */
+/* out [streams][T][W] = wte[tok] * scale + sinusoid(position); inv_freq: W / 2 (rounded up) 64-bit inverse frequencies */
+int llmss_embed_sinusoid(const int* tokens, const int* positions, const void* wte, const double* inv_freq, float* out, int T, int W,
+                         int vocab, float scale, int streams, int dtype, llmss_stream_t stream);
+/* xs [streams][T][W] in place: x_t <- sum_s mix[s][t] x_s + w_out[t] y (y null: no write); then out = rms_div(sum_s w_in[s] x_s)
+ * * norm_w (norm_w null: the sum itself; w_in null: no read-out) */
+int llmss_hyper_residual(float* xs, int T, int W, int streams, const float* y, int64_t ldy, const float* mix, const float* w_out,
+                         const float* w_in, const float* norm_w, float eps, void* out, int out_dtype, llmss_stream_t stream);
+/* S <- exp(log_decay) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  state [slots, heads, dv, dk]; unit_eps >= 0: q, k
+ * become unit vectors per head first; beta_sigmoid: beta is given before its sigmoid */
+int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv, const float* log_decay,
+                     int64_t ldg, const float* beta, int64_t ldb, float* out, float* state, const int* cu_q, const int* seq_lens,
+                     const int* slots, int B, int heads, int qk_heads, int dk, int dv, float unit_eps, float q_scale,
+                     int beta_sigmoid, llmss_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -720,6 +720,67 @@ def linear_scan(q, k, v, decay, decay_kind, batch, state, heads, qk_heads, dk, d
     return out
 
 
+_INV_FREQ = {}
+
+
+def _inv_freq(W: int, base: float, device):
+    """64-bit inverse frequencies base^(-2 i / W), i = 0 .. ceil(W / 2) - 1, kept per (width, base, device)."""
+    key = (W, float(base), str(device))
+    t = _INV_FREQ.get(key)
+    if t is None:
+        i = torch.arange((W + 1) // 2, dtype=torch.float64)
+        t = _INV_FREQ[key] = torch.pow(torch.tensor(float(base), dtype=torch.float64), -(2.0 * i) / W).to(device)
+    return t
+
+
+def embed_sinusoid(tokens, wte, scale, positions, streams=1, base=10000.0):
+    lib = _lib.load()
+    T = tokens.numel()
+    V, W = wte.shape
+    assert wte.is_contiguous()
+    out = torch.empty(streams, T, W, dtype=torch.float32, device=wte.device)
+    rc = lib.llmss_embed_sinusoid(_ptr(tokens), _ptr(positions), _ptr(wte), _ptr(_inv_freq(W, base, wte.device)), _ptr(out), T, W, V,
+                                  float(scale), int(streams), _DT[wte.dtype], _stream())
+    _lib.check(rc, "llmss_embed_sinusoid")
+    _count()
+    return out
+
+
+def hyper_residual(xs, y=None, mix=None, w_out=None, w_in=None, norm_w=None, eps=0.0, out_dtype=None):
+    lib = _lib.load()
+    assert xs.dtype == torch.float32 and xs.dim() == 3 and xs.is_contiguous()
+    S, T, W = xs.shape
+    ldy = 0
+    if y is not None:
+        _, Wy, ldy = _f32rows(y)
+        assert Wy == W and mix.dtype == torch.float32 and mix.is_contiguous() and mix.shape == (S, S) and w_out.numel() == S
+    dt = out_dtype or torch.float32
+    out = torch.empty(T, W, dtype=dt, device=xs.device) if w_in is not None else None
+    rc = lib.llmss_hyper_residual(_ptr(xs), T, W, S, _ptr(y), ldy, _ptr(mix), _ptr(w_out), _ptr(w_in), _ptr(norm_w), float(eps), _ptr(out),
+                                  _DT[dt], _stream())
+    _lib.check(rc, "llmss_hyper_residual")
+    _count()
+    return out
+
+
+def delta_scan(q, k, v, log_decay, beta, batch, state, heads, qk_heads, dk, dv, unit_eps=None, q_scale=1.0, beta_sigmoid=False):
+    lib = _lib.load()
+    T, _, ldv = _f32rows(v)
+    _, _, ldq = _f32rows(q)
+    _, _, ldk = _f32rows(k)
+    _, _, ldg = _f32rows(log_decay)
+    _, _, ldb = _f32rows(beta)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state[0].numel() == heads * dk * dv
+    out = torch.empty(T, heads * dv, dtype=torch.float32, device=v.device)
+    cu, sl, ss, B, _ = _bq(batch)
+    rc = lib.llmss_delta_scan(_ptr(q), ldq, _ptr(k), ldk, _ptr(v), ldv, _ptr(log_decay), ldg, _ptr(beta), ldb, _ptr(out), _ptr(state),
+                              cu, sl, ss, B, heads, qk_heads, dk, dv, -1.0 if unit_eps is None else float(unit_eps), float(q_scale),
+                              1 if beta_sigmoid else 0, _stream())
+    _lib.check(rc, "llmss_delta_scan")
+    _count()
+    return out
+
+
 def gated_rmsnorm(o, gate, gate_act, weight, groups, eps, gate_first, skip_x=None, skip_d=None, out_dtype=None):
     lib = _lib.load()
     T, C, ldo = _f32rows(o)
@@ -734,12 +795,22 @@ def gated_rmsnorm(o, gate, gate_act, weight, groups, eps, gate_first, skip_x=Non
 
 
 def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions, slot_mapping, k_cache, v_cache,
-                    out_dtype=None):
+                    out_dtype=None, norm_whole=False, v_norm=False, q_head_scale=None):
     lib = _lib.load()
     T, _, ld = _f32rows(qkv)
     dt = out_dtype or k_cache.dtype
-    assert k_cache.dtype == dt and v_cache.dtype == dt and k_cache.is_contiguous() and v_cache.is_contiguous()
+    if hkv > 0:
+        assert k_cache.dtype == dt and v_cache.dtype == dt and k_cache.is_contiguous() and v_cache.is_contiguous()
     q = torch.empty(T, hq * dk, dtype=dt, device=qkv.device)
+    if norm_whole or v_norm or q_head_scale is not None or hkv == 0:
+        # the general kernel (one CTA per token): norms over a token's whole projection, value norm, per-head factor, queries only
+        assert q_w.numel() == (hq * dk if norm_whole else dk) and (hkv == 0 or k_w.numel() == (hkv * dk if norm_whole else dk))
+        rc = lib.llmss_qkv_prepare(_ptr(qkv), ld, hq, hkv, dk, dv, _ptr(q_w), _ptr(k_w), float(eps), float(temp_coef), int(temp_every),
+                                   _ptr(q_head_scale), 1 if norm_whole else 0, 1 if v_norm else 0, _ptr(positions), _ptr(slot_mapping),
+                                   _ptr(k_cache), _ptr(v_cache), k_cache.shape[2] if hkv > 0 else 1, _ptr(q), T, _DT[dt], _stream())
+        _lib.check(rc, "llmss_qkv_prepare")
+        _count()
+        return q
     rc = lib.llmss_qknorm_kv_write(_ptr(qkv), ld, hq, hkv, dk, dv, _ptr(q_w), _ptr(k_w), float(eps), float(temp_coef), int(temp_every),
                                    _ptr(positions), _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), k_cache.shape[2], _ptr(q), T,
                                    _DT[dt], _stream())
@@ -766,12 +837,23 @@ def attention_bias_uses_tc(dtype, dk: int, dv: int, block_size: int, scale: floa
             and _lib.has("llmss_attn_prefill_paged_bias"))
 
 
-def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None):
+def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None,
+                   window=0, slopes=None):
     lib = _lib.load()
     T = q.shape[0]
     dt = q.dtype
     assert k_cache.dtype == dt and (out_dtype or dt) == dt and q.stride(1) == 1
     out = torch.empty(T, hq * dv, dtype=dt, device=q.device)
+    if window or slopes is not None:
+        # sliding window / linear distance penalty: the generic kernel, whose key loop starts at the window
+        rc = lib.llmss_attention_window(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
+                                        batch.block_tables.shape[1], k_cache.shape[2], _ptr(batch.seq_lens), _ptr(batch.cu_q),
+                                        _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _ptr(slopes), int(window or 0),
+                                        _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), batch.num_seqs,
+                                        max(1, batch.max_q), hq, hkv, dk, dv, float(scale), _DT[dt], _stream())
+        _lib.check(rc, "llmss_attention_window")
+        _count()
+        return out
     if dist_bias is not None and attention_bias_uses_tc(dt, dk, dv, k_cache.shape[2], scale) and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0:
         bs = k_cache.shape[2]
         if (batch.is_decode and _lib.has("llmss_attn_decode_tc_bias") and use_tc_decode(hq, hkv, dk, bs)
