@@ -72,42 +72,47 @@ def attention_keys_values(h, P, m, eps):
     return k.reshape(T, G, D), v_raw, v
 
 
+def head_slopes(H):
+    return np.array([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], F)
+
+
+def window_softmax(q, keys, values, factor, slopes, window):
+    """q [T, H, D], keys [T, G, D], values [T, G, Dv]: query i of head h sees keys j with 0 <= i - j < window (all j <= i without
+    a window); score = factor[h] q_i . k_j - slopes[h] (i - j); ordinary softmax; returns [T, H, Dv]."""
+    T, H, _ = q.shape
+    G = keys.shape[1]
+    out = np.zeros((T, H, values.shape[2]), F)
+    for hd in range(H):
+        g = hd // (H // G)
+        for i in range(T):
+            lo = 0 if window is None else max(0, i - window + 1)
+            js = np.arange(lo, i + 1)
+            s = (keys[js, g] @ q[i, hd]) * factor[hd] - slopes[hd] * (i - js)
+            p = np.exp(s - s.max())
+            p /= p.sum()
+            out[i, hd] = (p[:, None] * values[js, g]).sum(0)
+    return out
+
+
 def attention_mixer(h, P, m, eps, keys=None, values=None):
     """Windowed softmax attention.  ``keys`` / ``values`` given: the layer borrows them (and has no k / v tensors)."""
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, D = m["heads"], m["dim"]
     T = h.shape[0]
     q = causal_conv(h @ P["q"].T, P["q.conv"])
     q = (rms_div(q, eps) * P["q.norm"]).reshape(T, H, D)
     if keys is None:
         keys, _, values = attention_keys_values(h, P, m, eps)
     window = (m.get("mask") or {}).get("size")
-    gate = sigmoid(h @ P["g"].T)                             # [T, H]
-    out = np.zeros((T, H, Dv), F)
-    for hd in range(H):
-        g = hd // (H // G)
-        slope = 2.0 ** (-8.0 * (hd + 1) / H)
-        for i in range(T):
-            lo = 0 if window is None else max(0, i - window + 1)
-            js = np.arange(lo, i + 1)
-            s = (keys[js, g] @ q[i, hd]) * m["scale"] * P["temp"][hd] - slope * (i - js)
-            p = np.exp(s - s.max())
-            p /= p.sum()
-            out[i, hd] = (p[:, None] * values[js, g]).sum(0) * gate[i, hd]
-    return out.reshape(T, H * Dv) @ P["o"].T
+    out = window_softmax(q, keys, values, m["scale"] * P["temp"], head_slopes(H), window)
+    out = out * sigmoid(h @ P["g"].T)[:, :, None]            # one gate per head
+    return out.reshape(T, -1) @ P["o"].T
 
 
-def delta_mixer(h, P, m, eps, return_state=False):
-    """Gated delta rule, token by token."""
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    T = h.shape[0]
-    q = silu(causal_conv(h @ P["q"].T, P["q.conv"])).reshape(T, G, D)
-    k = silu(causal_conv(h @ P["k"].T, P["k.conv"])).reshape(T, G, D)
-    v = silu(causal_conv(h @ P["v"].T, P["v.conv"])).reshape(T, H, Dv)
-    q = q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) * D ** -0.5
-    k = k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)
-    beta = sigmoid(h @ P["b"].T)                             # [T, H]
-    decay = np.exp(-np.exp(P["A_log"]) * softplus(h @ P["a"].T + P["dt_bias"]))
-    gate = silu(h @ P["g"].T).reshape(T, H, Dv)
+def delta_rule(q, k, v, decay, beta):
+    """q, k [T, G, D], v [T, H, Dv], decay, beta [T, H].  Per head, token by token, in this order:
+    S <- decay S ;  u = beta (v - S^T k) ;  S <- S + k u^T ;  o = S^T q.  Returns (o [T, H, Dv], the last S [H, D, Dv])."""
+    T, H, Dv = v.shape
+    G, D = q.shape[1], q.shape[2]
     o = np.zeros((T, H, Dv), F)
     S = np.zeros((H, D, Dv), F)
     for t in range(T):
@@ -117,9 +122,24 @@ def delta_mixer(h, P, m, eps, return_state=False):
             u = beta[t, hd] * (v[t, hd] - S[hd].T @ k[t, g])
             S[hd] += np.outer(k[t, g], u)
             o[t, hd] = S[hd].T @ q[t, g]
-    y = rms_div(o, eps) * P["norm"] * gate
-    out = y.reshape(T, H * Dv) @ P["o"].T
-    return (out, S) if return_state else out
+    return o, S
+
+
+def unit(x, eps=1e-6):
+    return x / np.sqrt((x * x).sum(-1, keepdims=True) + eps)
+
+
+def delta_mixer(h, P, m, eps):
+    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    T = h.shape[0]
+    q = silu(causal_conv(h @ P["q"].T, P["q.conv"])).reshape(T, G, D)
+    k = silu(causal_conv(h @ P["k"].T, P["k.conv"])).reshape(T, G, D)
+    v = silu(causal_conv(h @ P["v"].T, P["v.conv"])).reshape(T, H, Dv)
+    beta = sigmoid(h @ P["b"].T)                             # [T, H]
+    decay = np.exp(-np.exp(P["A_log"]) * softplus(h @ P["a"].T + P["dt_bias"]))
+    o, _ = delta_rule(unit(q) * D ** -0.5, unit(k), v, decay, beta)
+    y = rms_div(o, eps) * P["norm"] * silu(h @ P["g"].T).reshape(T, H, Dv)
+    return y.reshape(T, H * Dv) @ P["o"].T
 
 
 def feed_forward(h, up, down):
@@ -180,3 +200,18 @@ def forward(tokens, cfg, tensors):
         after.append(xs.sum(0))
     x = rms_div(xs.sum(0), eps) * ten["final.norm"]
     return x @ ten["head"].T, np.stack(after)
+
+
+def load_weights(path):
+    """All tensors of a checkpoint folder as float64 arrays."""
+    from pathlib import Path
+
+    import torch
+    from safetensors import safe_open
+
+    out = {}
+    for f in sorted(Path(path).glob("*.safetensors")):
+        with safe_open(str(f), framework="pytorch") as h:
+            for k in h.keys():
+                out[k] = h.get_tensor(k).to(torch.float64).numpy()
+    return out
