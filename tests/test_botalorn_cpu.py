@@ -247,13 +247,13 @@ def test_window_edge_decides(window, device="cpu", dtype=torch.float32, tol=1e-4
                                            gate=gate[at:at + n].to(device), out_dtype=dtype, window=window or 0, slopes=slopes.to(device)))
             at += n
         close(torch.cat(rows), want, tol)
-    if window is not None and window < L:    # the test is sharp: one key more, or one less, is far outside the tolerance
+    if window is not None and window < L:    # the test is sharp: one key more, or one less, is far outside any tolerance used
         for off in (-1, 1):
             if window + off >= 1:
                 other = oracle.window_softmax(q.double().numpy(), k.double().numpy(), v.double().numpy(), np.full(H, 0.9),
                                               slopes.double().numpy(), window + off)
                 other = (other * oracle.sigmoid(gate.double().numpy())[:, :, None]).reshape(L, H * Dv)
-                assert np.abs(other - want).max() > 100 * tol * want.std()
+                assert np.abs(other - want).max() > 0.5 * want.std()
 
 
 @pytest.mark.parametrize("dk,dv,heads,qk_heads", [(10, 6, 4, 2), (16, 16, 2, 2), (5, 9, 3, 3), (24, 3, 1, 1), (40, 33, 2, 1)])
@@ -411,11 +411,11 @@ def test_steep_attention_over_windows_and_page_borders(tmp_path, device="cpu", d
     close(feed_in_portions(eng, "w", toks, [150]), want, tol * 3)
     close(feed_in_portions(eng, "p", toks, [31, 2, 36, 1, 1, 59, 2, 1]), want, tol * 3)
     close(feed_in_portions(eng, "d", toks, [100, 1]), want, tol * 3)
-    # the windows decide: one token more in every window moves the logits by far more than the tolerance
+    # the windows decide: one token more in every window moves the logits by a thousand times the 32-bit tolerance
     cfg2 = json.loads(json.dumps(cfg))
     for L in cfg2["layers"]:
         L["mixer"]["mask"]["size"] += 1
-    assert np.abs(want_logits(toks, cfg2, W) - want).max() > 50 * tol * want.std()
+    assert np.abs(want_logits(toks, cfg2, W) - want).max() > 0.3 * want.std()
 
 
 def test_first_tokens(tmp_path, device="cpu", dtype=torch.float32, tol=TOL):
