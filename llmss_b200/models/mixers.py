@@ -320,7 +320,7 @@ class WindowAttention:
         assert heads % kv_heads == 0, "window attention: query heads must be a multiple of key/value heads"
         self.own_kv = kv_from is None
         self.n_conv = heads * dim + ((kv_heads * dim + kv_heads * vdim) if self.own_kv else 0)
-        self.w_in = self.conv_w = self.q_norm = self.k_norm = self.temp = self.slopes = self.w_o = None
+        self.w_in = self.conv_w = self.q_norm = self.k_norm = self.temp = self.slopes = self.window_table = self.w_o = None
 
     def state_shapes(self):
         return {"conv": ((self.taps - 1, self.n_conv), F32)} if self.taps > 1 else {}
@@ -339,6 +339,11 @@ class WindowAttention:
         self.q_norm, self.k_norm, self.temp, self.w_o = q_norm, k_norm, temp, w_o.contiguous()
         H = self.heads
         self.slopes = torch.tensor([2.0 ** (-self.slope_exp * (h + 1) / H) for h in range(H)], dtype=F32, device=w_o.device)
+        # the window and the slopes as a distance table in raw-score units, for the tensor-core kernels (16-bit pages, equal key
+        # and value size 64 / 128 / 256); the generic kernel takes window and slopes themselves
+        self.window_table = (ops.window_bias_table(self.slopes, self.window, self.scale)
+                             if self.window and self.scale > 0 and w_o.is_cuda and w_o.dtype != F32 and self.dim == self.vdim
+                             and self.dim in (64, 128, 256) else None)
 
     def forward(self, h, batch, lc, dtype):
         """``lc``: this layer's cache view; its pages (``lc.k`` / ``lc.v``) are the lender's when keys and values are borrowed."""
@@ -355,7 +360,7 @@ class WindowAttention:
                                     norm_whole=True, v_norm=True, q_head_scale=self.temp)
         with trace("attention_bias"):
             ctx = ops.attention_bias(q, lc.k, lc.v, batch, H, G, D, Dv, self.scale, None, gate=gate, out_dtype=dtype,
-                                     window=self.window or 0, slopes=self.slopes)
+                                     window=self.window or 0, slopes=self.slopes, bias_over_scale=self.window_table)
         with trace("gemm_out"):
             return ops.linear(ctx, self.w_o, out_dtype=F32)
 

@@ -15,7 +15,7 @@ import torch
 
 from . import reference as ref
 from .reference import (DECAY_HEAD, DECAY_TOKEN_CHANNEL, DECAY_TOKEN_HEAD, GATE_NONE, GATE_SIGMOID, GATE_SILU, UNARY_NEG_EXP,
-                        UNARY_TANH, distance_bias_table)
+                        UNARY_TANH, distance_bias_table, window_bias_table)
 from .reference import (ACT_GELU_ERF, ACT_GELU_TANH, ACT_IDS, ACT_NONE, ACT_RELU, ACT_RELU2, ACT_SILU, NORM_DYT, NORM_LAYER,
                         NORM_RMS, ROPE_GPTJ, ROPE_NEOX, ROPE_NONE)
 

@@ -837,6 +837,9 @@ def attention_bias_uses_tc(dtype, dk: int, dv: int, block_size: int, scale: floa
             and _lib.has("llmss_attn_prefill_paged_bias"))
 
 
+from .reference import window_bias_table  # noqa: E402  (the window and slopes as a distance table)
+
+
 def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None,
                    window=0, slopes=None):
     lib = _lib.load()
@@ -844,24 +847,34 @@ def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias
     dt = q.dtype
     assert k_cache.dtype == dt and (out_dtype or dt) == dt and q.stride(1) == 1
     out = torch.empty(T, hq * dv, dtype=dt, device=q.device)
+    tc_ok = attention_bias_uses_tc(dt, dk, dv, k_cache.shape[2], scale) and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0
+    table = None
     if window or slopes is not None:
-        # sliding window / linear distance penalty: the generic kernel, whose key loop starts at the window
-        rc = lib.llmss_attention_window(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
-                                        batch.block_tables.shape[1], k_cache.shape[2], _ptr(batch.seq_lens), _ptr(batch.cu_q),
-                                        _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _ptr(slopes), int(window or 0),
-                                        _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), batch.num_seqs,
-                                        max(1, batch.max_q), hq, hkv, dk, dv, float(scale), _DT[dt], _stream())
-        _lib.check(rc, "llmss_attention_window")
-        _count()
-        return out
-    if dist_bias is not None and attention_bias_uses_tc(dt, dk, dv, k_cache.shape[2], scale) and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0:
+        # 16-bit pages of a tensor-core size with a window: the window and the slopes become a distance table whose last column
+        # hides the key (kept by the layer as ``bias_over_scale``, else derived here).  Everything else -- true 32-bit, other or
+        # unequal sizes, slopes without a window -- runs the generic kernel, whose key loop starts at the window.
+        if tc_ok and dist_bias is None and window and slopes is not None:
+            table = bias_over_scale if bias_over_scale is not None else window_bias_table(slopes, int(window), scale)
+            assert table.shape == (hq, int(window) + 1)
+        else:
+            rc = lib.llmss_attention_window(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
+                                            batch.block_tables.shape[1], k_cache.shape[2], _ptr(batch.seq_lens), _ptr(batch.cu_q),
+                                            _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _ptr(slopes),
+                                            int(window or 0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
+                                            batch.num_seqs, max(1, batch.max_q), hq, hkv, dk, dv, float(scale), _DT[dt], _stream())
+            _lib.check(rc, "llmss_attention_window")
+            _count()
+            return out
+    elif dist_bias is not None and tc_ok:
+        table = _bias_over_scale(dist_bias, scale, bias_over_scale)
+    if table is not None:
         bs = k_cache.shape[2]
         if (batch.is_decode and _lib.has("llmss_attn_decode_tc_bias") and use_tc_decode(hq, hkv, dk, bs)
                 and lib.llmss_attn_decode_tc_supported(hq, hkv, dk, bs)):
             # one query per sequence: the split-KV decode kernel (the q heads of a group are its MMA rows), then the gate
             splits = batch.decode_splits or decode_splits(batch.num_seqs, hq, hkv, dk, batch.max_kv, dt, bs)
             attn_decode(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, out, hq, hkv, dk, scale, splits,
-                        bias_over_scale=_bias_over_scale(dist_bias, scale, bias_over_scale))
+                        bias_over_scale=table)
             if gate is not None:
                 _lib.check(lib.llmss_head_gate(_ptr(out), out.stride(0), _ptr(gate), gate.stride(0), T, hq, dv, _DT[dt], _stream()),
                            "llmss_head_gate")
@@ -870,9 +883,8 @@ def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias
         rc = lib.llmss_attn_prefill_paged_bias(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
                                                batch.block_tables.shape[1], _ptr(batch.seq_lens), _ptr(out), out.stride(0),
                                                _ptr(batch.cu_q), batch.num_seqs, max(1, batch.max_q), T, hq, hkv, dk,
-                                               k_cache.shape[2], k_cache.shape[0], float(scale), _DT[dt],
-                                               _ptr(_bias_over_scale(dist_bias, scale, bias_over_scale)), dist_bias.shape[1], _ptr(gate),
-                                               gate.stride(0) if gate is not None else 0, _stream())
+                                               k_cache.shape[2], k_cache.shape[0], float(scale), _DT[dt], _ptr(table), table.shape[1],
+                                               _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
         _lib.check(rc, "llmss_attn_prefill_paged_bias")
         _count()
         return out

@@ -574,6 +574,19 @@ def distance_bias_table(rel, max_distance: int):
     return torch.stack(cols, dim=1).contiguous()
 
 
+MASKED_SCORE = -1.0e30      # a table entry that hides a key: its weight is exactly 0 beside any real score, and nothing overflows
+
+
+def window_bias_table(slopes, window: int, scale: float):
+    """A sliding window plus a linear distance penalty as a distance table in raw-score units (the form the tensor-core
+    attention kernels take): column d < window holds -slopes[h] * d / scale, the last column -- which those kernels use for
+    every distance from ``window`` on -- hides the key."""
+    d = torch.arange(window + 1, dtype=torch.float32, device=slopes.device)
+    tab = -(slopes.float()[:, None] * d[None, :]) / float(scale)
+    tab[:, window] = MASKED_SCORE
+    return tab.contiguous()
+
+
 def attention_bias(q, k_cache, v_cache, block_tables, seq_lens, cu_q, hq: int, hkv: int, dk: int, dv: int, scale: float,
                    dist_bias, gate=None, out_dtype=None, window: int = 0, slopes=None):
     """Causal softmax attention over the paged cache with key size dk, value size dv, grouped heads, an additive bias

@@ -219,12 +219,12 @@ def _paged(seq, bs, pages, dtype, device):
 
 
 @pytest.mark.parametrize("window", [1, 2, 16, 17, 33, 100, None])
-def test_window_edge_decides(window, device="cpu", dtype=torch.float32, tol=1e-4):
+def test_window_edge_decides(window, device="cpu", dtype=torch.float32, tol=1e-4, D=8, Dv=6, bs=16, L=70):
     """One key just inside and one just outside the window are made to win the softmax (scaled so that either would take
     nearly all the weight): the result is right only if exactly the keys with 0 <= i - j < window are seen.  Keys sit on
     both sides of page borders; queries are a prompt, a portion over prior context, and single decoded tokens."""
     torch.manual_seed(5)
-    H, G, D, Dv, L, bs = 4, 2, 8, 6, 70, 16
+    H, G, factor, pages = 4, 2, 0.9 * 8 / D, -(-L // bs)
     q, k, v = torch.randn(L, H, D), torch.randn(L, G, D), torch.randn(L, G, Dv)
     w = window or L
     for i in range(L):                       # key i - w + 1 (inside) and key i - w (outside) both match query i strongly
@@ -234,23 +234,23 @@ def test_window_edge_decides(window, device="cpu", dtype=torch.float32, tol=1e-4
     q, k, v = (x.to(dtype).float() for x in (q, k, v))      # what a 16-bit run is given, exactly
     slopes = torch.tensor(oracle.head_slopes(H), dtype=torch.float32)
     gate = torch.randn(L, H)
-    want = oracle.window_softmax(q.double().numpy(), k.double().numpy(), v.double().numpy(), np.full(H, 0.9), slopes.double().numpy(),
+    want = oracle.window_softmax(q.double().numpy(), k.double().numpy(), v.double().numpy(), np.full(H, factor), slopes.double().numpy(),
                                  window)
     want = (want * oracle.sigmoid(gate.double().numpy())[:, :, None]).reshape(L, H * Dv)
-    kc, table = _paged(k, bs, 5, dtype, device)
-    vc, _ = _paged(v, bs, 5, dtype, device)
-    for cuts in ([L], [33, 37], [50] + [1] * 20, [15, 2, 2, 30, 1, 20]):
+    kc, table = _paged(k, bs, pages, dtype, device)
+    vc, _ = _paged(v, bs, pages, dtype, device)
+    for cuts in ([L], [33, L - 33], [L - 20] + [1] * 20, [15, 2, 2, 30, 1, L - 50]):
         at, rows = 0, []
         for n in cuts:
             batch = BatchInput.build([[0] * n], [at], [table], bs, device, state_slots=[0])
-            rows.append(ops.attention_bias(q[at:at + n].reshape(n, H * D).to(dtype).to(device), kc, vc, batch, H, G, D, Dv, 0.9, None,
+            rows.append(ops.attention_bias(q[at:at + n].reshape(n, H * D).to(dtype).to(device), kc, vc, batch, H, G, D, Dv, factor, None,
                                            gate=gate[at:at + n].to(device), out_dtype=dtype, window=window or 0, slopes=slopes.to(device)))
             at += n
         close(torch.cat(rows), want, tol)
     if window is not None and window < L:    # the test is sharp: one key more, or one less, is far outside any tolerance used
         for off in (-1, 1):
             if window + off >= 1:
-                other = oracle.window_softmax(q.double().numpy(), k.double().numpy(), v.double().numpy(), np.full(H, 0.9),
+                other = oracle.window_softmax(q.double().numpy(), k.double().numpy(), v.double().numpy(), np.full(H, factor),
                                               slopes.double().numpy(), window + off)
                 other = (other * oracle.sigmoid(gate.double().numpy())[:, :, None]).reshape(L, H * Dv)
                 assert np.abs(other - want).max() > 0.5 * want.std()

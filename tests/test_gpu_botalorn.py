@@ -57,6 +57,42 @@ def test_window_edge(window):
     cases.test_window_edge_decides(window, "cuda", BF16, 5e-2)
 
 
+@pytest.mark.parametrize("d", [64, 128, 256])
+@pytest.mark.parametrize("window", [1, 2, 63, 64, 65, 128, 150, 1000])
+def test_window_edge_on_the_tensor_core_kernels(window, d):
+    """16-bit pages with key size = value size 64 / 128 / 256: the window and the slopes ride on the tensor-core kernels as a
+    distance table whose last column hides the key; the generic kernel on the same pages agrees."""
+    from llmss_b200.ops import cuda_impl as cu
+
+    assert cu.attention_bias_uses_tc(BF16, d, d, 64, 1.0)
+    n0 = cu._lib.LAUNCHES["count"]
+    cases.test_window_edge_decides(window, "cuda", BF16, 5e-2, D=d, Dv=d, bs=64, L=330)
+    cu._BIAS_TC = False
+    try:
+        cases.test_window_edge_decides(window, "cuda", BF16, 5e-2, D=d, Dv=d, bs=64, L=330)
+    finally:
+        cu._BIAS_TC = True
+    assert cu._lib.LAUNCHES["count"] > n0
+
+
+# key size = value size 64 / 128 in 16-bit: attention on the tensor-core kernels, lenders and borrowers with other windows
+cases.CONFIGS["tc_sizes"] = botalorn_config(128, 173, [
+    cases.att(heads=4, kv_heads=2, dim=64, vdim=64, conv=3, window=50, mlp={"ff": 128}),
+    cases.att(heads=2, kv_heads=1, dim=128, vdim=128, conv=2, window=100),
+    cases.dlt(heads=2, kv_heads=1, dim=64, vdim=64, conv=4),
+    cases.att(heads=4, kv_heads=2, dim=64, vdim=64, conv=2, window=64, kv_from=0),
+    cases.att(heads=2, kv_heads=1, dim=128, vdim=128, conv=4, window=7, kv_from=1, mlp={"ff": 128})], streams=2, embed_scale=11.0)
+
+
+def test_model_on_the_tensor_core_attention(tmp_path):
+    cases.test_whole_prompt_and_residual_stream(tmp_path / "a", "tc_sizes", "cuda", BF16, 8e-2)
+    cases.test_decode_token_by_token_and_portions(tmp_path / "b", "tc_sizes", "cuda", BF16, 8e-2)
+    cases.test_whole_prompt_and_residual_stream(tmp_path / "c", "tc_sizes", "cuda", F32, 3e-4)
+    cfg, W, gpu = cases.build(tmp_path / "d", "tc_sizes", "cuda", BF16, max_seq_len=1024)
+    toks = cases.tokens_for(cfg, 400, 5)
+    cases.close(cases.feed_in_portions(gpu, "p", toks, [250, 1, 1, 140, 1]), cases.want_logits(toks, cfg, W), 0.1)
+
+
 @pytest.mark.parametrize("dk,dv,heads,qk_heads", [(10, 6, 4, 2), (16, 16, 2, 2), (5, 9, 3, 3), (24, 3, 1, 1), (40, 33, 2, 1),
                                                   (64, 64, 2, 2), (128, 128, 4, 2), (136, 24, 2, 1), (48, 136, 1, 1), (300, 8, 2, 2)])
 def test_delta_scan_kernel(dk, dv, heads, qk_heads):
