@@ -574,7 +574,10 @@ def distance_bias_table(rel, max_distance: int):
     return torch.stack(cols, dim=1).contiguous()
 
 
-MASKED_SCORE = -1.0e30      # a table entry that hides a key: its weight is exactly 0 beside any real score, and nothing overflows
+# A scaled score that hides a key: exp(MASKED_SCORE - any real score) is exactly 0 in 32-bit, while the value is small enough
+# that the rounding of products with it stays far below 1 (a huge value would turn the rounding error of scale * score into a
+# huge exponent when a whole tile is hidden and the running maximum is the hidden score itself).
+MASKED_SCORE = -30000.0
 
 
 def window_bias_table(slopes, window: int, scale: float):
@@ -583,7 +586,7 @@ def window_bias_table(slopes, window: int, scale: float):
     every distance from ``window`` on -- hides the key."""
     d = torch.arange(window + 1, dtype=torch.float32, device=slopes.device)
     tab = -(slopes.float()[:, None] * d[None, :]) / float(scale)
-    tab[:, window] = MASKED_SCORE
+    tab[:, window] = MASKED_SCORE / float(scale)
     return tab.contiguous()
 
 
