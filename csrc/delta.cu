@@ -9,6 +9,12 @@
 // strips of KPT + 4 floats (the strips a warp reads together lie in different banks, every read a 16-byte one; strips beyond
 // dk hold zeros), made unit vectors there (x / sqrt(sum x^2 + eps), q times its scale), decays exp(log g) and write
 // strengths (sigmoid taken here if asked) beside them.  The state lies in memory column-major per head ([dv][dk]).
+// KPT is the key size itself up to 128 (R = 1): the lanes of a warp then differ only in their value column, every staged q / k
+// read is one address for the whole warp (a shared-memory broadcast), and no shuffle is needed; larger keys split over R lanes.
+//
+// A batch of single tokens (decode) runs the row-split form instead (delta_step_kernel): one warp per value column, lanes over
+// the key rows, so that every state access is one contiguous column (512 bytes at dk = 128) -- a decode step is bound by
+// reading and writing the states once.
 // Everything is 32-bit with full-precision exponentials.
 #include "common.cuh"
 
@@ -51,8 +57,21 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
   float* bs = gs + DTCH;             // [DTCH] write strengths
   float S[KPT];
   float* sp = a.state + (((int64_t)slot * a.H + h) * a.dv + (live ? j : 0)) * dk;
+  const bool vec = (dk & 3) == 0;        // every column of the state starts on a 16-byte boundary
 #pragma unroll
-  for (int ii = 0; ii < KPT; ++ii) S[ii] = (live && ctx > 0 && i0 + ii < dk) ? sp[i0 + ii] : 0.f;
+  for (int ii = 0; ii < KPT; ii += 4) {
+    float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && ctx > 0) {
+      if (vec && i0 + ii + 4 <= dk) t4 = *reinterpret_cast<const float4*>(sp + i0 + ii);
+      else {
+        if (i0 + ii < dk) t4.x = sp[i0 + ii];
+        if (i0 + ii + 1 < dk) t4.y = sp[i0 + ii + 1];
+        if (i0 + ii + 2 < dk) t4.z = sp[i0 + ii + 2];
+        if (i0 + ii + 3 < dk) t4.w = sp[i0 + ii + 3];
+      }
+    }
+    S[ii] = t4.x; S[ii + 1] = t4.y; S[ii + 2] = t4.z; S[ii + 3] = t4.w;
+  }
   for (int t0 = 0; t0 < ql; t0 += DTCH) {
     const int nt = min(DTCH, ql - t0);
     __syncthreads();
@@ -120,7 +139,92 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
   }
   if (live) {
 #pragma unroll
-    for (int ii = 0; ii < KPT; ++ii) if (i0 + ii < dk) sp[i0 + ii] = S[ii];
+    for (int ii = 0; ii < KPT; ii += 4) {
+      if (vec && i0 + ii + 4 <= dk) *reinterpret_cast<float4*>(sp + i0 + ii) = make_float4(S[ii], S[ii + 1], S[ii + 2], S[ii + 3]);
+      else {
+        if (i0 + ii < dk) sp[i0 + ii] = S[ii];
+        if (i0 + ii + 1 < dk) sp[i0 + ii + 1] = S[ii + 1];
+        if (i0 + ii + 2 < dk) sp[i0 + ii + 2] = S[ii + 2];
+        if (i0 + ii + 3 < dk) sp[i0 + ii + 3] = S[ii + 3];
+      }
+    }
+  }
+}
+
+// Single tokens: grid (B, H, column groups), 8 warps per block; warp w takes columns j0 + w, j0 + w + 8, ... four at a time.
+// Lane l holds rows l, l + 32, ... (KL of them) of q, k and of the column in flight.
+constexpr int STEP_WARPS = 8, STEP_COLS = 4;
+template <int KL>
+__global__ void __launch_bounds__(STEP_WARPS * 32) delta_step_kernel(DeltaArgs a, int cols_per_block) {
+  const int b = blockIdx.x;
+  const int q0 = a.cu_q[b], ql = a.cu_q[b + 1] - q0, ctx = a.seq_lens[b] - ql, slot = a.slots[b];
+  if (slot < 0 || ctx < 0 || ql != 1) return;
+  const int h = blockIdx.y, hk = h / a.rep, dk = a.dk, dv = a.dv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t t = q0;
+  float qv[KL], kv[KL];
+  float sq = 0.f, sk = 0.f;
+#pragma unroll
+  for (int m = 0; m < KL; ++m) {
+    const int i = lane + 32 * m;
+    qv[m] = i < dk ? a.q[t * a.ldq + (int64_t)hk * dk + i] : 0.f;
+    kv[m] = i < dk ? a.k[t * a.ldk + (int64_t)hk * dk + i] : 0.f;
+    sq = fmaf(qv[m], qv[m], sq);
+    sk = fmaf(kv[m], kv[m], sk);
+  }
+  if (a.unit || a.q_scale != 1.f) {
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float rq = (a.unit ? rsqrtf(sq + a.unit_eps) : 1.f) * a.q_scale, rk = a.unit ? rsqrtf(sk + a.unit_eps) : 1.f;
+#pragma unroll
+    for (int m = 0; m < KL; ++m) { qv[m] *= rq; kv[m] *= rk; }
+  }
+  const float g = expf(a.log_decay[t * a.ldg + h]);
+  const float braw = a.beta[t * a.ldb + h];
+  const float be = a.beta_sigmoid ? 1.f / (1.f + expf(-braw)) : braw;
+  float* sp = a.state + ((int64_t)slot * a.H + h) * dv * dk;
+  const float* vp = a.v + t * a.ldv + (int64_t)h * dv;
+  float* op = a.out + t * a.H * dv + (int64_t)h * dv;
+  const int j0 = blockIdx.z * cols_per_block, j1 = min(dv, j0 + cols_per_block);
+  for (int jb = j0 + warp; jb < j1; jb += STEP_WARPS * STEP_COLS) {
+    float S[STEP_COLS][KL], d[STEP_COLS], e[STEP_COLS];
+#pragma unroll
+    for (int c = 0; c < STEP_COLS; ++c) {
+      const int j = jb + c * STEP_WARPS;
+      d[c] = 0.f;
+#pragma unroll
+      for (int m = 0; m < KL; ++m) {
+        const int i = lane + 32 * m;
+        S[c][m] = (j < j1 && ctx > 0 && i < dk) ? sp[(int64_t)j * dk + i] : 0.f;
+        d[c] = fmaf(S[c][m], kv[m], d[c]);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int c = 0; c < STEP_COLS; ++c) d[c] += __shfl_xor_sync(0xffffffffu, d[c], o);
+#pragma unroll
+    for (int c = 0; c < STEP_COLS; ++c) {
+      const int j = jb + c * STEP_WARPS;
+      const float u = be * ((j < j1 ? vp[j] : 0.f) - g * d[c]);
+      e[c] = 0.f;
+#pragma unroll
+      for (int m = 0; m < KL; ++m) {
+        S[c][m] = fmaf(g, S[c][m], kv[m] * u);
+        e[c] = fmaf(S[c][m], qv[m], e[c]);
+        const int i = lane + 32 * m;
+        if (j < j1 && i < dk) sp[(int64_t)j * dk + i] = S[c][m];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int c = 0; c < STEP_COLS; ++c) e[c] += __shfl_xor_sync(0xffffffffu, e[c], o);
+#pragma unroll
+    for (int c = 0; c < STEP_COLS; ++c) {
+      const int j = jb + c * STEP_WARPS;
+      if (lane == 0 && j < j1) op[j] = e[c];
+    }
   }
 }
 
@@ -130,8 +234,8 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
 // out [T, heads * dv]; state [slots, heads, dv, dk].  unit_eps >= 0: q and k become x / sqrt(sum x^2 + unit_eps) per head first.
 LLMSS_API int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv,
                                const float* log_decay, int64_t ldg, const float* beta, int64_t ldb, float* out, float* state,
-                               const int* cu_q, const int* seq_lens, const int* slots, int B, int heads, int qk_heads, int dk, int dv,
-                               float unit_eps, float q_scale, int beta_sigmoid, cudaStream_t stream) {
+                               const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, int heads, int qk_heads, int dk,
+                               int dv, float unit_eps, float q_scale, int beta_sigmoid, cudaStream_t stream) {
   LLMSS_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0, "delta_scan: %d value heads over %d query/key heads", heads, qk_heads);
   LLMSS_REQUIRE(dk > 0 && dk <= 1024 && dv > 0, "delta_scan: key size %d (at most 1024), value size %d", dk, dv);
   if (B <= 0) return 0;
@@ -140,7 +244,25 @@ LLMSS_API int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int6
   a.out = out; a.state = state; a.cu_q = cu_q; a.seq_lens = seq_lens; a.slots = slots;
   a.H = heads; a.rep = heads / qk_heads; a.dk = dk; a.dv = dv;
   a.unit = unit_eps >= 0.f ? 1 : 0; a.unit_eps = unit_eps >= 0.f ? unit_eps : 0.f; a.q_scale = q_scale; a.beta_sigmoid = beta_sigmoid;
-  const int kpt = dk <= 8 ? 8 : (dk <= 16 ? 16 : 32);
+  if (max_q <= 1 && dk <= 256) {
+    // every sequence brings one token: one warp per value column, lanes over the key rows
+    a.R = 1; a.dvt = 0;
+    const int per_pass = STEP_WARPS * STEP_COLS;
+    int groups = 1;
+    while ((int64_t)B * heads * groups < 1024 && groups * per_pass < dv) groups *= 2;
+    int cols = (dv + groups - 1) / groups;
+    cols = ((cols + per_pass - 1) / per_pass) * per_pass;
+    const dim3 sgrid(B, heads, (dv + cols - 1) / cols);
+    LLMSS_REQUIRE(sgrid.y <= 65535 && sgrid.z <= 65535, "delta_scan: grid too large");
+    const int kl = (dk + 31) / 32;
+    if (kl <= 1) delta_step_kernel<1><<<sgrid, STEP_WARPS * 32, 0, stream>>>(a, cols);
+    else if (kl <= 2) delta_step_kernel<2><<<sgrid, STEP_WARPS * 32, 0, stream>>>(a, cols);
+    else if (kl <= 4) delta_step_kernel<4><<<sgrid, STEP_WARPS * 32, 0, stream>>>(a, cols);
+    else delta_step_kernel<8><<<sgrid, STEP_WARPS * 32, 0, stream>>>(a, cols);
+    LLMSS_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
+  const int kpt = dk <= 8 ? 8 : (dk <= 16 ? 16 : (dk <= 32 ? 32 : (dk <= 64 ? 64 : 128)));
   int R = 1;
   while (R * kpt < dk) R *= 2;
   a.R = R;
@@ -158,7 +280,9 @@ LLMSS_API int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int6
   } while (0)
   if (kpt == 8) LLMSS_DS(8);
   else if (kpt == 16) LLMSS_DS(16);
-  else LLMSS_DS(32);
+  else if (kpt == 32) LLMSS_DS(32);
+  else if (kpt == 64) LLMSS_DS(64);
+  else LLMSS_DS(128);
 #undef LLMSS_DS
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;

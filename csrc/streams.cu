@@ -124,10 +124,18 @@ __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__
   if (norm_w != nullptr) r = rsqrtf(block_sum256(ss, red) / W + eps);
   // every thread re-reads only the columns it wrote itself
   for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
+    float v[VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      const float v = norm_w != nullptr ? us[c + e] * r * norm_w[c + e] : us[c + e];
-      out[t * W + c + e] = from_f32<T>(v);
+    for (int e = 0; e < VEC; ++e) v[e] = norm_w != nullptr ? us[c + e] * r * norm_w[c + e] : us[c + e];
+    if constexpr (VEC == 4) {
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(out + t * W + c) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+      } else {
+        __align__(8) T tmp[4] = {from_f32<T>(v[0]), from_f32<T>(v[1 % VEC]), from_f32<T>(v[2 % VEC]), from_f32<T>(v[3 % VEC])};
+        *reinterpret_cast<uint2*>(out + t * W + c) = *reinterpret_cast<const uint2*>(tmp);
+      }
+    } else {
+      out[t * W + c] = from_f32<T>(v[0]);
     }
   }
 }

@@ -335,10 +335,11 @@ int llmss_embed_sinusoid(const int* tokens, const int* positions, const void* wt
 int llmss_hyper_residual(float* xs, int T, int W, int streams, const float* y, int64_t ldy, const float* mix, const float* w_out,
                          const float* w_in, const float* norm_w, float eps, void* out, int out_dtype, llmss_stream_t stream);
 /* S <- exp(log_decay) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  state [slots, heads, dv, dk]; unit_eps >= 0: q, k
- * become unit vectors per head first; beta_sigmoid: beta is given before its sigmoid */
+ * become unit vectors per head first; beta_sigmoid: beta is given before its sigmoid; max_q <= 1 (every sequence brings one
+ * token) selects the form with one warp per state column */
 int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v, int64_t ldv, const float* log_decay,
                      int64_t ldg, const float* beta, int64_t ldb, float* out, float* state, const int* cu_q, const int* seq_lens,
-                     const int* slots, int B, int heads, int qk_heads, int dk, int dv, float unit_eps, float q_scale,
+                     const int* slots, int B, int max_q, int heads, int qk_heads, int dk, int dv, float unit_eps, float q_scale,
                      int beta_sigmoid, llmss_stream_t stream);
 
 #ifdef __cplusplus

@@ -772,9 +772,9 @@ def delta_scan(q, k, v, log_decay, beta, batch, state, heads, qk_heads, dk, dv, 
     _, _, ldb = _f32rows(beta)
     assert state.dtype == torch.float32 and state.is_contiguous() and state[0].numel() == heads * dk * dv
     out = torch.empty(T, heads * dv, dtype=torch.float32, device=v.device)
-    cu, sl, ss, B, _ = _bq(batch)
+    cu, sl, ss, B, mq = _bq(batch)
     rc = lib.llmss_delta_scan(_ptr(q), ldq, _ptr(k), ldk, _ptr(v), ldv, _ptr(log_decay), ldg, _ptr(beta), ldb, _ptr(out), _ptr(state),
-                              cu, sl, ss, B, heads, qk_heads, dk, dv, -1.0 if unit_eps is None else float(unit_eps), float(q_scale),
+                              cu, sl, ss, B, mq, heads, qk_heads, dk, dv, -1.0 if unit_eps is None else float(unit_eps), float(q_scale),
                               1 if beta_sigmoid else 0, _stream())
     _lib.check(rc, "llmss_delta_scan")
     _count()
