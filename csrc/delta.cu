@@ -7,9 +7,9 @@
 // in two warp-shuffle sums per token.  One block = one (sequence, head, slice of value columns); the block that reads a
 // slot's old state is the block that writes its new one.  Tokens are staged 16 at a time through shared memory: q and k in
 // strips of KPT + 4 floats (the strips a warp reads together lie in different banks, every read a 16-byte one; strips beyond
-// dk hold zeros), made unit vectors there (x / sqrt(sum x^2 + eps), q times its scale), decays exp(log g) and write
+// dk hold zeros), copied asynchronously one stage ahead, made unit vectors there (x / sqrt(sum x^2 + eps), q times its scale), decays exp(log g) and write
 // strengths (sigmoid taken here if asked) beside them.  The state lies in memory column-major per head ([dv][dk]).
-// KPT is the key size itself up to 128 (R = 1): the lanes of a warp then differ only in their value column, every staged q / k
+// KPT is the key size itself up to 64 (R = 1): the lanes of a warp then differ only in their value column, every staged q / k
 // read is one address for the whole warp (a shared-memory broadcast), and no shuffle is needed; larger keys split over R lanes.
 //
 // A batch of single tokens (decode) runs the row-split form instead (delta_step_kernel): one warp per value column, lanes over
@@ -34,8 +34,21 @@ struct DeltaArgs {
   int H, rep, dk, dv, dvt, R;
   float unit_eps, q_scale;
   int unit, beta_sigmoid;
+  int vec16;       // q / k / v rows, the key size and the value slices allow 16-byte copies
 };
 
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Stages of 16 tokens are double-buffered: the asynchronous copies of stage s + 1 (global -> shared, no registers) run behind the
+// arithmetic of stage s, so the dependent chain of a long portion never waits for memory.
 template <int KPT>
 __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
   constexpr int STRIP = KPT + 4;
@@ -50,11 +63,7 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
   const bool live = jl < nj;
   const int j = j0 + jl, i0 = r * KPT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = nthr >> 5;
-  float* qs = sm;                    // [DTCH][row]
-  float* ks = qs + DTCH * row;       // [DTCH][row]
-  float* vs = ks + DTCH * row;       // [DTCH][dvt]
-  float* gs = vs + DTCH * a.dvt;     // [DTCH] decays
-  float* bs = gs + DTCH;             // [DTCH] write strengths
+  const int stage_floats = 2 * DTCH * row + DTCH * a.dvt + 2 * DTCH;     // q, k [DTCH][row]; v [DTCH][dvt]; decays, strengths [DTCH]
   float S[KPT];
   float* sp = a.state + (((int64_t)slot * a.H + h) * a.dv + (live ? j : 0)) * dk;
   const bool vec = (dk & 3) == 0;        // every column of the state starts on a 16-byte boundary
@@ -72,27 +81,69 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
     }
     S[ii] = t4.x; S[ii + 1] = t4.y; S[ii + 2] = t4.z; S[ii + 3] = t4.w;
   }
-  for (int t0 = 0; t0 < ql; t0 += DTCH) {
+  // the strips' padding (beyond dk, and between strips) is read by the arithmetic and never copied into: zero it once
+  for (int idx = threadIdx.x; idx < 2 * stage_floats; idx += nthr) sm[idx] = 0.f;
+  __syncthreads();
+  auto issue = [&](int t0, float* B) {
     const int nt = min(DTCH, ql - t0);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * row; idx += nthr) {
-      const int tt = idx / row, w = idx % row, ii = w % STRIP, c = (w / STRIP) * KPT + ii;
-      const bool ok = ii < KPT && c < dk;
-      const int64_t t = q0 + t0 + tt;
-      qs[idx] = ok ? a.q[t * a.ldq + (int64_t)hk * dk + c] : 0.f;
-      ks[idx] = ok ? a.k[t * a.ldk + (int64_t)hk * dk + c] : 0.f;
-    }
-    for (int idx = threadIdx.x; idx < nt * a.dvt; idx += nthr) {
-      const int tt = idx / a.dvt, c = idx % a.dvt;
-      vs[idx] = c < nj ? a.v[(int64_t)(q0 + t0 + tt) * a.ldv + (int64_t)h * a.dv + j0 + c] : 0.f;
+    float* qs = B;
+    float* ks = B + DTCH * row;
+    float* vs = ks + DTCH * row;
+    float* gs = vs + DTCH * a.dvt;
+    if (a.vec16) {
+      const int n4 = dk >> 2;
+      for (int idx = threadIdx.x; idx < nt * n4; idx += nthr) {
+        const int tt = idx / n4, c = (idx - tt * n4) << 2;
+        const int dst = tt * row + (c / KPT) * STRIP + c % KPT;
+        const int64_t t = q0 + t0 + tt;
+        cp_async_16(qs + dst, a.q + t * a.ldq + (int64_t)hk * dk + c);
+        cp_async_16(ks + dst, a.k + t * a.ldk + (int64_t)hk * dk + c);
+      }
+      const int v4 = nj >> 2;       // vec16: dv and the slice width are multiples of 4
+      for (int idx = threadIdx.x; idx < nt * v4; idx += nthr) {
+        const int tt = idx / v4, c = (idx - tt * v4) << 2;
+        cp_async_16(vs + tt * a.dvt + c, a.v + (int64_t)(q0 + t0 + tt) * a.ldv + (int64_t)h * a.dv + j0 + c);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < nt * dk; idx += nthr) {
+        const int tt = idx / dk, c = idx - tt * dk;
+        const int dst = tt * row + (c / KPT) * STRIP + c % KPT;
+        const int64_t t = q0 + t0 + tt;
+        cp_async_4(qs + dst, a.q + t * a.ldq + (int64_t)hk * dk + c);
+        cp_async_4(ks + dst, a.k + t * a.ldk + (int64_t)hk * dk + c);
+      }
+      for (int idx = threadIdx.x; idx < nt * nj; idx += nthr) {
+        const int tt = idx / nj, c = idx - tt * nj;
+        cp_async_4(vs + tt * a.dvt + c, a.v + (int64_t)(q0 + t0 + tt) * a.ldv + (int64_t)h * a.dv + j0 + c);
+      }
     }
     if (threadIdx.x < nt) {
       const int64_t t = q0 + t0 + threadIdx.x;
-      gs[threadIdx.x] = expf(a.log_decay[t * a.ldg + h]);
-      const float bb = a.beta[t * a.ldb + h];
-      bs[threadIdx.x] = a.beta_sigmoid ? 1.f / (1.f + expf(-bb)) : bb;
+      cp_async_4(gs + threadIdx.x, a.log_decay + t * a.ldg + h);
+      cp_async_4(gs + DTCH + threadIdx.x, a.beta + t * a.ldb + h);
+    }
+    cp_async_commit();
+  };
+  issue(0, sm);
+  int cur = 0;
+  for (int t0 = 0; t0 < ql; t0 += DTCH, cur ^= 1) {
+    const int nt = min(DTCH, ql - t0);
+    float* qs = sm + cur * stage_floats;
+    float* ks = qs + DTCH * row;
+    float* vs = ks + DTCH * row;
+    float* gs = vs + DTCH * a.dvt;
+    float* bs = gs + DTCH;
+    if (t0 + DTCH < ql) {
+      issue(t0 + DTCH, sm + (cur ^ 1) * stage_floats);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
+    if (threadIdx.x < nt) {
+      gs[threadIdx.x] = expf(gs[threadIdx.x]);
+      if (a.beta_sigmoid) bs[threadIdx.x] = 1.f / (1.f + expf(-bs[threadIdx.x]));
+    }
     if (a.unit || a.q_scale != 1.f) {
       for (int tt = warp; tt < nt; tt += nwarp) {
         float sq = 0.f, sk = 0.f;
@@ -108,8 +159,8 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
           ks[tt * row + w] *= rk;
         }
       }
-      __syncthreads();
     }
+    __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
       const float g = gs[tt], be = bs[tt];
       const float* kr = ks + tt * row + r * STRIP;
@@ -136,6 +187,7 @@ __global__ void __launch_bounds__(256) delta_scan_kernel(DeltaArgs a) {
       for (int s = R >> 1; s > 0; s >>= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
       if (live && r == 0) a.out[(int64_t)(q0 + t0 + tt) * a.H * a.dv + (int64_t)h * a.dv + j] = o;
     }
+    __syncthreads();      // this buffer is copied into again at the start of the next round
   }
   if (live) {
 #pragma unroll
@@ -262,7 +314,10 @@ LLMSS_API int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int6
     LLMSS_CHECK_CUDA(cudaGetLastError());
     return 0;
   }
-  const int kpt = dk <= 8 ? 8 : (dk <= 16 ? 16 : (dk <= 32 ? 32 : (dk <= 64 ? 64 : 128)));
+  // key rows per thread: the key size itself up to 64 (a column per thread), 64 beyond (R lanes per column)
+  static const int kpt_max = [] { const char* e = getenv("LLMSS_DELTA_KPT"); const int v = e ? atoi(e) : 64; return v == 32 || v == 128 ? v : 64; }();
+  int kpt = dk <= 8 ? 8 : (dk <= 16 ? 16 : (dk <= 32 ? 32 : (dk <= 64 ? 64 : 128)));
+  if (kpt > kpt_max) kpt = kpt_max;
   int R = 1;
   while (R * kpt < dk) R *= 2;
   a.R = R;
@@ -271,7 +326,9 @@ LLMSS_API int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int6
   a.dvt = threads / R;
   const dim3 grid(B, heads, (dv + a.dvt - 1) / a.dvt);
   LLMSS_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "delta_scan: grid too large");
-  const size_t smem = sizeof(float) * ((size_t)2 * DTCH * R * (kpt + 4) + (size_t)DTCH * a.dvt + 2 * DTCH);
+  a.vec16 = (dk % 4 == 0 && dv % 4 == 0 && a.dvt % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 &&
+             (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0) ? 1 : 0;
+  const size_t smem = 2 * sizeof(float) * ((size_t)2 * DTCH * R * (kpt + 4) + (size_t)DTCH * a.dvt + 2 * DTCH);
 #define LLMSS_DS(K)                                                                     \
   do {                                                                                  \
     static PerDeviceSmem gsm;                                                           \

@@ -42,8 +42,9 @@ __device__ __forceinline__ float block_sum256(float v, float* red) {
   return t;
 }
 
-// one block per token row; VEC = 4: rows are read and written as float4 (W a multiple of 4, 16-byte aligned bases)
-template <typename T, int VEC>
+// one block per token row; VEC = 4: rows are read and written as float4 (W a multiple of 4, 16-byte aligned bases); NS: the
+// largest stream count of the instantiation (1, 2, 4 or HS_MAX: the per-thread arrays stay as small as the model's streams)
+template <typename T, int VEC, int NS>
 __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__ xs, int64_t Ttot, int W, int S,
                                                              const float* __restrict__ y, int64_t ldy, const float* __restrict__ mix,
                                                              const float* __restrict__ w_out, const float* __restrict__ w_in,
@@ -59,9 +60,9 @@ __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__
   const int64_t t = blockIdx.x;
   float ss = 0.f;
   for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
-    float x[HS_MAX][VEC], yv[VEC], u[VEC];
+    float x[NS][VEC], yv[VEC];
 #pragma unroll
-    for (int s = 0; s < HS_MAX; ++s) {
+    for (int s = 0; s < NS; ++s) {
       if (s >= S) break;
       const float* p = xs + ((int64_t)s * Ttot + t) * W + c;
       if constexpr (VEC == 4) {
@@ -79,15 +80,15 @@ __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__
       } else {
         yv[0] = p[0];
       }
-      float n[HS_MAX][VEC];
+      float n[NS][VEC];
 #pragma unroll
-      for (int d = 0; d < HS_MAX; ++d) {
+      for (int d = 0; d < NS; ++d) {
         if (d >= S) break;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           float acc = 0.f;
 #pragma unroll
-          for (int s = 0; s < HS_MAX; ++s) {
+          for (int s = 0; s < NS; ++s) {
             if (s >= S) break;
             acc = fmaf(cm[s * S + d], x[s][e], acc);
           }
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__
         }
       }
 #pragma unroll
-      for (int d = 0; d < HS_MAX; ++d) {
+      for (int d = 0; d < NS; ++d) {
         if (d >= S) break;
         float* p2 = xs + ((int64_t)d * Ttot + t) * W + c;
         if constexpr (VEC == 4) *reinterpret_cast<float4*>(p2) = make_float4(n[d][0], n[d][1 % VEC], n[d][2 % VEC], n[d][3 % VEC]);
@@ -109,11 +110,10 @@ __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__
       for (int e = 0; e < VEC; ++e) {
         float acc = 0.f;
 #pragma unroll
-        for (int s = 0; s < HS_MAX; ++s) {
+        for (int s = 0; s < NS; ++s) {
           if (s >= S) break;
           acc = fmaf(ci[s], x[s][e], acc);
         }
-        u[e] = acc;
         us[c + e] = acc;
         ss = fmaf(acc, acc, ss);
       }
@@ -164,15 +164,23 @@ LLMSS_API int llmss_hyper_residual(float* xs, int T_, int W, int streams, const 
   LLMSS_REQUIRE(smem <= 200 * 1024, "hyper_residual: width %d exceeds shared memory", W);
   const bool vec = W % 4 == 0 && ((uintptr_t)xs & 15) == 0 && (y == nullptr || (((uintptr_t)y & 15) == 0 && ldy % 4 == 0));
   const int threads = W >= 1024 ? 256 : 128;
-#define LLMSS_HR(TT, V)                                                                                          \
-  do {                                                                                                           \
-    static PerDeviceSmem gsm;                                                                                    \
-    if (smem > 48 * 1024) LLMSS_CHECK_CUDA(gsm.ensure(hyper_residual_kernel<TT, V>, (int)smem));                 \
-    hyper_residual_kernel<TT, V><<<T_, threads, smem, stream>>>(xs, (int64_t)T_, W, streams, y, ldy, mix, w_out, \
-                                                                w_in, norm_w, eps, (TT*)out);                    \
+#define LLMSS_HR(TT, V, N)                                                                                          \
+  do {                                                                                                              \
+    static PerDeviceSmem gsm;                                                                                       \
+    if (smem > 48 * 1024) LLMSS_CHECK_CUDA(gsm.ensure(hyper_residual_kernel<TT, V, N>, (int)smem));                 \
+    hyper_residual_kernel<TT, V, N><<<T_, threads, smem, stream>>>(xs, (int64_t)T_, W, streams, y, ldy, mix, w_out, \
+                                                                   w_in, norm_w, eps, (TT*)out);                    \
   } while (0)
-  if (vec) LLMSS_BY_DTYPE(out_dtype, LLMSS_HR(T, 4));
-  else LLMSS_BY_DTYPE(out_dtype, LLMSS_HR(T, 1));
+#define LLMSS_HR_N(TT, V)                      \
+  do {                                         \
+    if (streams <= 1) LLMSS_HR(TT, V, 1);      \
+    else if (streams <= 2) LLMSS_HR(TT, V, 2); \
+    else if (streams <= 4) LLMSS_HR(TT, V, 4); \
+    else LLMSS_HR(TT, V, HS_MAX);              \
+  } while (0)
+  if (vec) LLMSS_BY_DTYPE(out_dtype, LLMSS_HR_N(T, 4));
+  else LLMSS_BY_DTYPE(out_dtype, LLMSS_HR_N(T, 1));
+#undef LLMSS_HR_N
 #undef LLMSS_HR
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
