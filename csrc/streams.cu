@@ -13,7 +13,7 @@
 
 namespace {
 
-constexpr int HS_MAX = 8;     // streams
+constexpr int HS_MAX = 16;    // streams
 
 template <typename T>
 __global__ void __launch_bounds__(256) embed_sinusoid_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
@@ -43,7 +43,7 @@ __device__ __forceinline__ float block_sum256(float v, float* red) {
 }
 
 // one block per token row; VEC = 4: rows are read and written as float4 (W a multiple of 4, 16-byte aligned bases); NS: the
-// largest stream count of the instantiation (1, 2, 4 or HS_MAX: the per-thread arrays stay as small as the model's streams)
+// largest stream count of the instantiation (1, 2, 4, 8 or HS_MAX: the per-thread arrays stay as small as the model's streams)
 template <typename T, int VEC, int NS>
 __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__ xs, int64_t Ttot, int W, int S,
                                                              const float* __restrict__ y, int64_t ldy, const float* __restrict__ mix,
@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256) hyper_residual_kernel(float* __restrict__
                                                              const float* __restrict__ norm_w, float eps, T* __restrict__ out) {
   extern __shared__ __align__(16) float us[];     // [W] the read-out before its norm
   __shared__ float red[32], cm[HS_MAX * HS_MAX], co[HS_MAX], ci[HS_MAX];
-  if (threadIdx.x < S * S && y != nullptr) cm[threadIdx.x] = mix[threadIdx.x];
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) cm[i] = y != nullptr ? mix[i] : 0.f;
   if (threadIdx.x < S) {
     co[threadIdx.x] = y != nullptr ? w_out[threadIdx.x] : 0.f;
     ci[threadIdx.x] = w_in != nullptr ? w_in[threadIdx.x] : 0.f;
@@ -176,6 +176,7 @@ LLMSS_API int llmss_hyper_residual(float* xs, int T_, int W, int streams, const 
     if (streams <= 1) LLMSS_HR(TT, V, 1);      \
     else if (streams <= 2) LLMSS_HR(TT, V, 2); \
     else if (streams <= 4) LLMSS_HR(TT, V, 4); \
+    else if (streams <= 8) LLMSS_HR(TT, V, 8); \
     else LLMSS_HR(TT, V, HS_MAX);              \
   } while (0)
   if (vec) LLMSS_BY_DTYPE(out_dtype, LLMSS_HR_N(T, 4));

@@ -128,7 +128,7 @@ def test_embedding_with_sinusoid(W, streams, scale, device="cpu", dtype=torch.fl
         close(xs[s], want, tol)
 
 
-@pytest.mark.parametrize("S,W", [(1, 24), (2, 32), (3, 50), (5, 7)])
+@pytest.mark.parametrize("S,W", [(1, 24), (2, 32), (3, 50), (5, 7), (11, 20)])
 def test_hyper_residual_op(S, W, device="cpu", out_dtype=torch.float32, tol=1e-5):
     """Write only, read only, both at once, the read-out without a norm; the write takes every stream from the OLD ones."""
     torch.manual_seed(S * 100 + W)
@@ -219,12 +219,12 @@ def _paged(seq, bs, pages, dtype, device):
 
 
 @pytest.mark.parametrize("window", [1, 2, 16, 17, 33, 100, None])
-def test_window_edge_decides(window, device="cpu", dtype=torch.float32, tol=1e-4, D=8, Dv=6, bs=16, L=70):
+def test_window_edge_decides(window, device="cpu", dtype=torch.float32, tol=1e-4, D=8, Dv=6, bs=16, L=70, H=4, G=2):
     """One key just inside and one just outside the window are made to win the softmax (scaled so that either would take
     nearly all the weight): the result is right only if exactly the keys with 0 <= i - j < window are seen.  Keys sit on
     both sides of page borders; queries are a prompt, a portion over prior context, and single decoded tokens."""
     torch.manual_seed(5)
-    H, G, factor, pages = 4, 2, 0.9 * 8 / D, -(-L // bs)
+    factor, pages = 0.9 * 8 / D, -(-L // bs)
     q, k, v = torch.randn(L, H, D), torch.randn(L, G, D), torch.randn(L, G, Dv)
     w = window or L
     for i in range(L):                       # key i - w + 1 (inside) and key i - w (outside) both match query i strongly

@@ -39,7 +39,7 @@ def test_stream_kernels():
     for W, S, scale in [(32, 1, 1.0), (50, 3, 12.0), (7, 2, 0.5), (1024, 2, 32.0)]:
         cases.test_embedding_with_sinusoid(W, S, scale, "cuda", F32, 1e-5)
         cases.test_embedding_with_sinusoid(W, S, scale, "cuda", BF16, 1e-5)      # the table is exact in 16 bits, the sum 32-bit
-    for S, W in [(1, 24), (2, 32), (3, 50), (5, 7), (8, 36), (2, 2048)]:
+    for S, W in [(1, 24), (2, 32), (3, 50), (5, 7), (8, 36), (11, 20), (16, 64), (2, 2048)]:
         cases.test_hyper_residual_op(S, W, "cuda", F32, 1e-5)
         cases.test_hyper_residual_op(S, W, "cuda", BF16, 2e-2)
     cases.test_token_shift_carries_the_previous_row("cuda")
@@ -73,6 +73,14 @@ def test_window_edge_on_the_tensor_core_kernels(window, d):
     finally:
         cu._BIAS_TC = True
     assert cu._lib.LAUNCHES["count"] > n0
+
+
+@pytest.mark.parametrize("H,G", [(2, 2), (8, 1), (6, 3)])
+def test_window_edge_on_the_tensor_core_kernels_by_group_size(H, G):
+    """One query head per key/value head, and eight: the decode kernel's row packing differs."""
+    for window in (64, 150):
+        cases.test_window_edge_decides(window, "cuda", BF16, 8e-2, D=128, Dv=128, bs=64, L=330, H=H, G=G)
+        cases.test_window_edge_decides(window, "cuda", BF16, 8e-2, D=64, Dv=64, bs=64, L=200, H=H, G=G)
 
 
 # key size = value size 64 / 128 in 16-bit: attention on the tensor-core kernels, lenders and borrowers with other windows
