@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(256) postnorm_kernel(const float* __restrict__
 }
 
 // ------------------------------------------------------------------------------------------------ token_shift
-template <typename T>
+// VEC = 4: four columns per thread, 16-byte loads and 8- / 16-byte stores (W, ldx multiples of 4, 16-byte aligned bases)
+template <typename T, int VEC>
 __global__ void __launch_bounds__(128) token_shift_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ mu,
                                                           int S, T* __restrict__ out, int64_t Ttot, int W,
                                                           const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
@@ -117,13 +118,44 @@ __global__ void __launch_bounds__(128) token_shift_kernel(const float* __restric
   const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
   for (int j = blockIdx.y; j < s.ql; j += gridDim.y) {
     const int64_t t = s.q0 + j;
-    for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < W; c += gridDim.z * blockDim.x) {
-      const float cur = x[t * ldx + c];
-      const float prev = j > 0 ? x[(t - 1) * ldx + c] : (s.ctx > 0 ? prev_state[(int64_t)s.slot * W + c] : 0.f);
-      const float d = prev - cur;
-      for (int k = 0; k < S; ++k) out[((int64_t)k * Ttot + t) * W + c] = from_f32<T>(fmaf(d, mu[(int64_t)k * W + c], cur));
-      // the thread that read column c of the old row is the one that replaces it
-      if (j == 0 && blockIdx.y == 0) prev_state[(int64_t)s.slot * W + c] = x[(int64_t)(s.q0 + s.ql - 1) * ldx + c];
+    for (int c = (blockIdx.z * blockDim.x + threadIdx.x) * VEC; c < W; c += gridDim.z * blockDim.x * VEC) {
+      float cur[VEC], d[VEC];
+      if constexpr (VEC == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(x + t * ldx + c);
+        const float4 p = j > 0 ? *reinterpret_cast<const float4*>(x + (t - 1) * ldx + c)
+                               : (s.ctx > 0 ? *reinterpret_cast<const float4*>(prev_state + (int64_t)s.slot * W + c)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f));
+        cur[0] = a.x; cur[1 % VEC] = a.y; cur[2 % VEC] = a.z; cur[3 % VEC] = a.w;
+        d[0] = p.x - a.x; d[1 % VEC] = p.y - a.y; d[2 % VEC] = p.z - a.z; d[3 % VEC] = p.w - a.w;
+      } else {
+        cur[0] = x[t * ldx + c];
+        const float prev = j > 0 ? x[(t - 1) * ldx + c] : (s.ctx > 0 ? prev_state[(int64_t)s.slot * W + c] : 0.f);
+        d[0] = prev - cur[0];
+      }
+      for (int k = 0; k < S; ++k) {
+        T* o = out + ((int64_t)k * Ttot + t) * W + c;
+        const float* m = mu + (int64_t)k * W + c;
+        if constexpr (VEC == 4) {
+          const float4 m4 = *reinterpret_cast<const float4*>(m);
+          const float v0 = fmaf(d[0], m4.x, cur[0]), v1 = fmaf(d[1 % VEC], m4.y, cur[1 % VEC]), v2 = fmaf(d[2 % VEC], m4.z, cur[2 % VEC]),
+                      v3 = fmaf(d[3 % VEC], m4.w, cur[3 % VEC]);
+          if constexpr (sizeof(T) == 4) {
+            *reinterpret_cast<float4*>(o) = make_float4(v0, v1, v2, v3);
+          } else {
+            __align__(8) T tmp[4] = {from_f32<T>(v0), from_f32<T>(v1), from_f32<T>(v2), from_f32<T>(v3)};
+            *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(tmp);
+          }
+        } else {
+          o[0] = from_f32<T>(fmaf(d[0], m[0], cur[0]));
+        }
+      }
+      // the thread that read columns c .. of the old row is the one that replaces them
+      if (j == 0 && blockIdx.y == 0) {
+        const float* last = x + (int64_t)(s.q0 + s.ql - 1) * ldx + c;
+        float* st = prev_state + (int64_t)s.slot * W + c;
+        if constexpr (VEC == 4) *reinterpret_cast<float4*>(st) = *reinterpret_cast<const float4*>(last);
+        else st[0] = last[0];
+      }
     }
   }
 }
@@ -159,6 +191,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restric
       const int jj = j0 - hist + i;
       win[i] = i >= hist ? 0.f : (jj >= 0 ? u[(int64_t)(s.q0 + jj) * ldu + c] : old[i]);
     }
+#pragma unroll 8
     for (int j = j0; j < j1; ++j) {
       const float cur = u[(int64_t)(s.q0 + j) * ldu + c];
       float acc = bv;
@@ -182,6 +215,75 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restric
           for (int k = 0; k < kMaxTaps; ++k) if (k == i + s.ql) v = old[k];
         }
         st[(int64_t)i * C] = v;
+      }
+    }
+  }
+}
+
+// The same with four neighbouring channels per thread: 16-byte loads and stores (C and ldu multiples of 4, 16-byte aligned
+// bases); grid (B, ceil(C / 512), token chunks of CH tokens: shorter chunks than the scalar form, for enough blocks).
+template <int kMaxTaps, int CH>
+__global__ void __launch_bounds__(128) causal_conv4_kernel(const float* __restrict__ u, int64_t ldu, const float* __restrict__ w,
+                                                           const float* __restrict__ bias, float* __restrict__ out, int C, int taps,
+                                                           int act, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
+                                                           const int* __restrict__ slots, float* __restrict__ state) {
+  const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
+  const int c = (blockIdx.y * 128 + threadIdx.x) * 4;
+  if (c >= C) return;
+  const int hist = taps - 1;
+  float wt[kMaxTaps][4];
+  float4 win[kMaxTaps], old[kMaxTaps];
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < kMaxTaps; ++i) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) wt[i][e] = i < taps ? w[(int64_t)(c + e) * taps + i] : 0.f;
+    old[i] = zero;
+  }
+  const float4 bv = bias != nullptr ? *reinterpret_cast<const float4*>(bias + c) : zero;
+  float* st = state != nullptr && s.slot >= 0 ? state + ((int64_t)s.slot * hist) * C + c : nullptr;
+  for (int z = blockIdx.z; z * CH < s.ql; z += gridDim.z) {
+    const int j0 = z * CH, j1 = min(s.ql, j0 + CH);
+    if (z == 0 && st != nullptr && s.ctx > 0) {
+#pragma unroll
+      for (int i = 0; i < kMaxTaps; ++i) if (i < hist) old[i] = *reinterpret_cast<const float4*>(st + (int64_t)i * C);
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxTaps; ++i) {
+      const int jj = j0 - hist + i;
+      win[i] = i >= hist ? zero : (jj >= 0 ? *reinterpret_cast<const float4*>(u + (int64_t)(s.q0 + jj) * ldu + c) : old[i]);
+    }
+    const float* up = u + (int64_t)(s.q0 + j0) * ldu + c;
+    float* op = out + (int64_t)(s.q0 + j0) * C + c;
+#pragma unroll 4
+    for (int j = j0; j < j1; ++j, up += ldu, op += C) {
+      const float4 cur = *reinterpret_cast<const float4*>(up);
+      float4 acc = bv;
+#pragma unroll
+      for (int i = 0; i < kMaxTaps; ++i) {
+        if (i < taps) {
+          const float4 v = i < hist ? win[i] : cur;
+          acc.x = fmaf(wt[i][0], v.x, acc.x); acc.y = fmaf(wt[i][1], v.y, acc.y);
+          acc.z = fmaf(wt[i][2], v.z, acc.z); acc.w = fmaf(wt[i][3], v.w, acc.w);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxTaps - 1; ++i) win[i] = i + 1 < hist ? win[i + 1] : cur;
+      *reinterpret_cast<float4*>(op) = make_float4(act_exact(acc.x, act), act_exact(acc.y, act), act_exact(acc.z, act), act_exact(acc.w, act));
+    }
+    if (z == 0 && st != nullptr) {
+      // new tail: inputs ql - hist .. ql - 1; those before this step's first row come from the old tail
+#pragma unroll
+      for (int i = 0; i < kMaxTaps; ++i) {
+        if (i >= hist) continue;
+        const int jj = s.ql - hist + i;
+        float4 v = zero;
+        if (jj >= 0) v = *reinterpret_cast<const float4*>(u + (int64_t)(s.q0 + jj) * ldu + c);
+        else {
+#pragma unroll
+          for (int k = 0; k < kMaxTaps; ++k) if (k == i + s.ql) v = old[k];
+        }
+        *reinterpret_cast<float4*>(st + (int64_t)i * C) = v;
       }
     }
   }
@@ -862,9 +964,15 @@ LLMSS_API int llmss_token_shift(const float* x, int64_t ldx, const float* mu, in
                                 cudaStream_t stream) {
   if (B <= 0 || T_ <= 0) return 0;
   // a decode batch has one row per sequence: spread its columns over blocks instead
-  const dim3 grid(B, max(1, min(max_q, 256)), max_q < 8 ? max(1, min((W + 255) / 256, 32)) : 1);
-  LLMSS_BY_DTYPE(dtype, (token_shift_kernel<T><<<grid, 128, 0, stream>>>(x, ldx, mu, S, (T*)out, (int64_t)T_, W, cu_q, seq_lens, slots,
-                                                                         prev_state)));
+  const bool vec = W % 4 == 0 && ldx % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)mu) | ((uintptr_t)out) | ((uintptr_t)prev_state)) & 15) == 0;
+  const int per_block = vec ? 512 : 128;       // columns one block covers per pass
+  const dim3 grid(B, max(1, min(max_q, 1024)), max_q < 8 ? max(1, min((W + per_block - 1) / per_block, 32)) : 1);
+  if (vec)
+    LLMSS_BY_DTYPE(dtype, (token_shift_kernel<T, 4><<<grid, 128, 0, stream>>>(x, ldx, mu, S, (T*)out, (int64_t)T_, W, cu_q, seq_lens, slots,
+                                                                              prev_state)));
+  else
+    LLMSS_BY_DTYPE(dtype, (token_shift_kernel<T, 1><<<grid, 128, 0, stream>>>(x, ldx, mu, S, (T*)out, (int64_t)T_, W, cu_q, seq_lens, slots,
+                                                                              prev_state)));
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -875,7 +983,16 @@ LLMSS_API int llmss_causal_conv(const float* u, int64_t ldu, const float* w, con
   LLMSS_REQUIRE(taps >= 1 && taps <= kMaxTapsAny, "causal_conv: %d taps (1..%d)", taps, kMaxTapsAny);
   LLMSS_REQUIRE(taps == 1 || state != nullptr, "causal_conv: more than one tap needs a state");
   if (B <= 0 || T_ <= 0) return 0;
-  const dim3 grid(B, (C + 127) / 128, max(1, min((max_q + kConvChunk - 1) / kConvChunk, 64)));
+  const int chunks = max(1, min((max_q + kConvChunk - 1) / kConvChunk, 64));
+  if (taps <= 4 && C % 4 == 0 && ldu % 4 == 0 &&
+      ((((uintptr_t)u) | ((uintptr_t)out) | ((uintptr_t)bias) | ((uintptr_t)state)) & 15) == 0) {
+    // (a null bias or state is aligned; the state's rows are C floats apart)
+    const dim3 grid4(B, (C / 4 + 127) / 128, max(1, min((max_q + 15) / 16, 128)));
+    causal_conv4_kernel<4, 16><<<grid4, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+    LLMSS_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
+  const dim3 grid(B, (C + 127) / 128, chunks);
   if (taps <= 4) causal_conv_kernel<4><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
   else if (taps <= 8) causal_conv_kernel<8><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
   else causal_conv_kernel<16><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
