@@ -89,7 +89,7 @@ def _build_mixer(kind: str, m: dict, width: int, eps: float):
     window = mask.get("size")
     kv_from = m.get("kv_from")
     return WindowAttention(width, int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), int(m.get("conv", 1)),
-                           float(m["scale"]), None if window is None else int(window), eps,
+                           float(m.get("scale", int(m["dim"]) ** -0.5)), None if window is None else int(window), eps,
                            kv_from=None if kv_from is None else int(kv_from))
 
 
@@ -197,22 +197,28 @@ def _f32(t):
     return t.float().contiguous()
 
 
-def _load_attention(mx: WindowAttention, get, p):
+def _taps_from_tensor(mx, shape):
+    """The number of taps is the convolution tensor's second size (the configuration's ``conv`` only repeats it)."""
+    mx.taps = int(shape[1])
+
+
+def _load_attention(mx: WindowAttention, get, w_shape, p):
     """<p>.q [heads*dim, W] + .q.conv [.., taps] + .q.norm [heads*dim]; <p>.temp [heads]; <p>.g [heads, W]; <p>.o [W, heads*vdim];
     with projections of its own also <p>.k [kv_heads*dim, W] + .k.conv + .k.norm [kv_heads*dim], <p>.v [kv_heads*vdim, W] + .v.conv."""
     own = mx.own_kv
+    _taps_from_tensor(mx, w_shape(f"{p}.q.conv"))
     mx.set_weights(get(f"{p}.q"), get(f"{p}.k") if own else None, get(f"{p}.v") if own else None,
                    _f32(get(f"{p}.q.conv")), _f32(get(f"{p}.k.conv")) if own else None, _f32(get(f"{p}.v.conv")) if own else None,
                    _f32(get(f"{p}.q.norm")), _f32(get(f"{p}.k.norm")) if own else None, _f32(get(f"{p}.temp")), get(f"{p}.g"),
                    get(f"{p}.o"))
-    want = mx.n_conv
-    if mx.conv_w.shape != (want, mx.taps):
-        raise ValueError(f"{p}: convolution weights {tuple(mx.conv_w.shape)} do not fit {want} channels x {mx.taps} taps")
+    if mx.conv_w.shape != (mx.n_conv, mx.taps):
+        raise ValueError(f"{p}: convolution weights {tuple(mx.conv_w.shape)} do not fit {mx.n_conv} channels x {mx.taps} taps")
 
 
-def _load_delta(mx: DeltaMixer, get, p):
+def _load_delta(mx: DeltaMixer, get, w_shape, p):
     """<p>.q / .k [kv_heads*dim, W], <p>.v / .g [heads*vdim, W], each of q k v with .conv [.., taps]; <p>.b / .a [heads, W];
     <p>.dt_bias / .A_log [heads]; <p>.norm [vdim]; <p>.o [W, heads*vdim]."""
+    _taps_from_tensor(mx, w_shape(f"{p}.q.conv"))
     mx.set_weights(get(f"{p}.q"), get(f"{p}.k"), get(f"{p}.v"), _f32(get(f"{p}.q.conv")), _f32(get(f"{p}.k.conv")),
                    _f32(get(f"{p}.v.conv")), get(f"{p}.b"), get(f"{p}.a"), _f32(get(f"{p}.dt_bias")), _f32(get(f"{p}.A_log")),
                    _f32(get(f"{p}.norm")), get(f"{p}.g"), get(f"{p}.o"))
@@ -226,8 +232,14 @@ _LOADERS = {"attention": _load_attention, "delta": _load_delta}
 def load_botalorn(m: BotalornLM, w):
     get = w.get_tensor
 
+    streams = m.spec.streams
+    if streams is None and w.has("l0.hc1.in"):
+        # hyper-connection tensors without the configuration key: their size says how many streams there are
+        streams = int(w.get_shape("l0.hc1.in")[0])
+        m.n_streams, m.sum_in = streams, torch.ones(streams, dtype=F32, device=m.device)
+
     def connection(prefix):
-        if m.spec.streams is None:
+        if streams is None:
             return HyperConnection.identity(m.device)
         return HyperConnection(_f32(get(f"{prefix}.in")), _f32(get(f"{prefix}.mix")), _f32(get(f"{prefix}.out")))
 
@@ -237,7 +249,7 @@ def load_botalorn(m: BotalornLM, w):
         L.norm1 = _f32(get(f"{p}.norm1"))
         L.shift = _f32(get(f"{p}.shift")).view(1, -1) if w.has(f"{p}.shift") else None
         L.hc1 = connection(f"{p}.hc1")
-        _LOADERS[L.kind](L.mixer, get, f"{p}.mix")
+        _LOADERS[L.kind](L.mixer, get, w.get_shape, f"{p}.mix")
         if L.ffn is None:
             continue
         L.norm2 = _f32(get(f"{p}.norm2"))
