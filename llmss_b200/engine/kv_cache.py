@@ -126,12 +126,19 @@ class HybridCache:
     ``slot`` of all of them from its first token to its release (``SlotAllocator``).  States are not cleared when a slot
     changes hands: the kernels start from zeros whenever a sequence's first row is its position 0.
 
-    ``kv_layers``: {layer key: (kv_heads, dk, dv)}; ``states``: {(layer key, name): (shape, dtype)}."""
+    A third kind of page serves latent-attention layers: one row ``[num_blocks, block_size, width]`` per token (the layout
+    of ``LatentCache``), through the same block tables.
 
-    def __init__(self, kv_layers, states, num_blocks: int, block_size: int, num_slots: int, dtype, device):
+    ``kv_layers``: {layer key: (kv_heads, dk, dv)}; ``states``: {(layer key, name): (shape, dtype)}; ``latents``:
+    {layer key: row width}."""
+
+    def __init__(self, kv_layers, states, num_blocks: int, block_size: int, num_slots: int, dtype, device, latents=None):
         self.num_blocks, self.block_size, self.num_slots = num_blocks, block_size, num_slots
         self.kv_layers = dict(kv_layers)
-        self.num_layers = len(self.kv_layers)
+        self.latent_layers = dict(latents or {})
+        self.num_layers = len(self.kv_layers) + len(self.latent_layers)
+        self.lplanes = {key: torch.zeros(num_blocks, block_size, w, dtype=dtype, device=device)
+                        for key, w in self.latent_layers.items()}
         self.kplanes = {key: torch.zeros(num_blocks, h, block_size, dk, dtype=dtype, device=device)
                         for key, (h, dk, dv) in self.kv_layers.items()}
         self.vplanes = {key: torch.zeros(num_blocks, h, block_size, dv, dtype=dtype, device=device)
@@ -144,12 +151,16 @@ class HybridCache:
     def v(self, layer) -> torch.Tensor:
         return self.vplanes[layer]
 
+    def latent(self, layer) -> torch.Tensor:
+        return self.lplanes[layer]
+
     def state(self, layer, name: str) -> torch.Tensor:
         return self.states[(layer, name)]
 
     @staticmethod
-    def bytes_per_block(kv_layers, block_size, dtype) -> int:
-        return sum(h * (dk + dv) for h, dk, dv in kv_layers.values()) * block_size * torch.empty((), dtype=dtype).element_size()
+    def bytes_per_block(kv_layers, block_size, dtype, latents=None) -> int:
+        per_token = sum(h * (dk + dv) for h, dk, dv in kv_layers.values()) + sum((latents or {}).values())
+        return per_token * block_size * torch.empty((), dtype=dtype).element_size()
 
     def state_bytes_per_slot(self) -> int:
         return sum(t[0].numel() * t.element_size() for t in self.states.values())
@@ -159,6 +170,8 @@ class HybridCache:
         for key in self.kplanes:
             self.kplanes[key][dst:dst + n] = old.kplanes[key][src:src + n]
             self.vplanes[key][dst:dst + n] = old.vplanes[key][src:src + n]
+        for key in self.lplanes:
+            self.lplanes[key][dst:dst + n] = old.lplanes[key][src:src + n]
         for key, t in self.states.items():
             t.copy_(old.states[key])
 

@@ -21,6 +21,7 @@ from .botalorn import BotalornLM, botalorn_spec, load_botalorn
 from .decoder import DecoderLM
 from .families import FAMILIES
 from .ninelix import NinelixLM, load_ninelix, ninelix_spec
+from .zenorax import ZenoraxLM, load_zenorax, zenorax_spec
 
 
 class PagedState:
@@ -165,6 +166,21 @@ class BotalornForCausalLM(CausalLM):
         self.core.finalize()
 
 
+class ZenoraxForCausalLM(CausalLM):
+    """Native architecture (see models/zenorax.py): sub-layers normed on both sides, input convolutions, depth-weighted
+    averaging of layer outputs, latent attention with a rotated key part, sink attention, a gated linear recurrence.  Same
+    constructor and forward interface as the HF-shaped classes."""
+    family = "zenorax"
+    float32_on_cuda = True
+
+    def __init__(self, config, weights, fuse_parallel: bool = True):
+        nn.Module.__init__(self)
+        self.config = config
+        self.core = ZenoraxLM(zenorax_spec(config), weights.process_group, weights.device, weights.dtype)
+        load_zenorax(self.core, weights)
+        self.core.finalize()
+
+
 MODEL_REGISTRY = {
     "gptj": GPTJForCausalLM,
     "gpt_bigcode": GPTBigCodeForCausalLM,
@@ -174,4 +190,5 @@ MODEL_REGISTRY = {
     "bedovik": BedovikForCausalLM,
     "ninelix": NinelixForCausalLM,
     "botalorn": BotalornForCausalLM,
+    "zenorax": ZenoraxForCausalLM,
 }

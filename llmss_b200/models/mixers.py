@@ -10,6 +10,9 @@
   * ``WindowAttention`` -- grouped-query softmax attention over a sliding window with a linear distance penalty per head,
     query / key norm over the whole projection, a value norm, a factor per query head and a per-head output gate; a
     layer may attend over the pages another layer writes;
+  * ``SinkAttention`` -- grouped-query softmax attention whose values are the projected keys, with rotary positions from
+    a frequency table, unit-RMS queries / keys and a learned sink logit per head in the softmax denominator;
+  * ``Hgrn2Mixer`` -- a gated linear recurrence whose forget gate (bounded from below) also sets the write strength;
   * ``DeltaMixer`` -- the gated delta rule (ops.delta_scan) behind short convolutions, with a gated per-head norm;
   * ``HyperConnection`` -- the read / mix / write weights of one sub-layer over several residual streams;
   * ``DenseFFN``.
@@ -26,8 +29,8 @@ import math
 import torch
 
 from .. import ops
-from ..ops import (ACT_GELU_ERF, ACT_NONE, ACT_SILU, DECAY_HEAD, DECAY_TOKEN_CHANNEL, DECAY_TOKEN_HEAD, GATE_SIGMOID, GATE_SILU,
-                   UNARY_NEG_EXP, UNARY_TANH)
+from ..ops import (ACT_GELU_ERF, ACT_NONE, ACT_SILU, DECAY_HEAD, DECAY_TOKEN_CHANNEL, DECAY_TOKEN_HEAD, GATE_NONE, GATE_SIGMOID,
+                   GATE_SILU, UNARY_NEG_EXP, UNARY_TANH)
 from ..utils.tracing import trace
 
 F32 = torch.float32
@@ -46,6 +49,10 @@ class LayerCacheView:
 
     def sub(self, prefix: str) -> "LayerCacheView":
         return LayerCacheView(self.cache, self.key, self.prefix + prefix)
+
+    @property
+    def latent(self):
+        return self.cache.latent(self.pages_key)
 
     @property
     def k(self):
@@ -363,6 +370,102 @@ class WindowAttention:
                                      window=self.window or 0, slopes=self.slopes, bias_over_scale=self.window_table)
         with trace("gemm_out"):
             return ops.linear(ctx, self.w_o, out_dtype=F32)
+
+
+class SinkAttention:
+    """Grouped-query softmax attention whose values are the keys as projected (there is no value projection), with an
+    attention sink.
+
+        q, k = W h ;  v = k                                          (v: before rotation and norm)
+        q, k <- rotate(q, k) on the first 2 len(freq) channels of every head, pairs (i, i + n) (or interleaved)
+        q, k <- rms_div per head (no weight), if ``unit_norm``
+        p_ij = exp(scale q_i . k_j) / (sum_(j' <= i) exp(scale q_i . k_j') + exp(sink_h)) ;  o_i = sum_j p_ij v_j ;  W_o
+
+    The rotation is a frequency table and a magnitude (ops.rotary_frequencies): linear interpolation, YaRN or none are
+    tables.  Cached: prepared keys (K pages) and projected keys (V pages).  One input GEMM over the stacked rows [q | k]."""
+
+    def __init__(self, width, heads, kv_heads, dim, scale, eps, freq, mag=1.0, interleaved=False, unit_norm=True):
+        self.width, self.heads, self.kv_heads, self.dim, self.scale, self.eps = width, heads, kv_heads, dim, scale, eps
+        self.freq, self.mag, self.interleaved, self.unit_norm = freq, mag, interleaved, unit_norm
+        assert heads % kv_heads == 0, "sink attention: query heads must be a multiple of key/value heads"
+        assert 2 * freq.numel() <= dim, "sink attention: more rotated channels than the head has"
+        self.w_in = self.sinks = self.w_o = None
+
+    def state_shapes(self):
+        return {}
+
+    def kv_shape(self):
+        return (self.kv_heads, self.dim, self.dim)
+
+    def latent_width(self):
+        return None
+
+    def weights(self):
+        return [self.w_in, self.sinks, self.w_o]
+
+    def set_weights(self, wq, wk, sinks, w_o):
+        self.w_in = torch.cat([wq, wk], dim=0).contiguous()
+        self.sinks, self.w_o = sinks, w_o.contiguous()
+
+    def forward(self, h, batch, lc, dtype):
+        H, G, D = self.heads, self.kv_heads, self.dim
+        with trace("gemm_in"):
+            y = ops.linear(h, self.w_in, out_dtype=F32)
+        with trace("rope_norm_kv_write"):
+            q = ops.rope_norm_kv_write(y, H, G, D, self.freq, self.mag, self.interleaved, self.unit_norm, self.eps, batch.positions,
+                                       batch.slot_mapping, lc.k, lc.v, out_dtype=dtype)
+        with trace("attention_sink"):
+            ctx = ops.attention_bias(q, lc.k, lc.v, batch, H, G, D, D, self.scale, None, out_dtype=dtype, sinks=self.sinks)
+        with trace("gemm_out"):
+            return ops.linear(ctx, self.w_o, out_dtype=F32)
+
+
+class Hgrn2Mixer:
+    """Gated linear recurrence in which the forget gate also decides what is written (HGRN2).
+
+        q = silu(W_q h) ;  v = W_v h ;  f = lower + (1 - lower) sigmoid(W_f h + b_f)          per head and key channel
+        S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T ;  o_t = S_t^T q_t
+        out = W_o concat_h(rms_div(o_h) * norm)                                              norm [vdim] shared by the heads
+
+    It is ops.linear_scan with key = 1 - f and a per-channel decay f (given as ln f).  State per sequence: S (32-bit).
+    One input GEMM over the stacked rows [q | f | v]."""
+
+    def __init__(self, width, heads, dim, vdim, eps):
+        self.width, self.heads, self.dim, self.vdim, self.eps = width, heads, dim, vdim, eps
+        self.n_qk = heads * dim
+        self.w_in = self.b_in = self.lower = self.norm_w = self.w_o = None
+
+    def state_shapes(self):
+        return {"S": ((self.heads, self.dim, self.vdim), F32)}
+
+    def kv_shape(self):
+        return None
+
+    def latent_width(self):
+        return None
+
+    def weights(self):
+        return [self.w_in, self.b_in, self.lower, self.norm_w, self.w_o]
+
+    def set_weights(self, wq, wf, bf, wv, lower, norm_w, w_o):
+        self.w_in = torch.cat([wq, wf, wv], dim=0).contiguous()
+        zq, zv = torch.zeros(wq.shape[0], dtype=bf.dtype, device=bf.device), torch.zeros(wv.shape[0], dtype=bf.dtype, device=bf.device)
+        self.b_in = torch.cat([zq, bf, zv]).contiguous()
+        self.lower, self.w_o = lower, w_o.contiguous()
+        self.norm_w = norm_w.repeat(self.heads).contiguous()
+
+    def forward(self, h, batch, lc, dtype):
+        H, D, Dv, n = self.heads, self.dim, self.vdim, self.n_qk
+        with trace("gemm_in"):
+            y = ops.linear(h, self.w_in, self.b_in, out_dtype=F32)
+        with trace("hgrn_gates"):
+            q, k, logf = ops.hgrn_gates(y, n, self.lower)
+        with trace("linear_scan"):
+            o = ops.linear_scan(q, k, y[:, 2 * n:], logf, DECAY_TOKEN_CHANNEL, batch, lc.state("S"), H, H, D, Dv)
+        with trace("gated_rmsnorm"):
+            z = ops.gated_rmsnorm(o, None, GATE_NONE, self.norm_w, H, self.eps, False, out_dtype=dtype)
+        with trace("gemm_out"):
+            return ops.linear(z, self.w_o, out_dtype=F32)
 
 
 class DeltaMixer:

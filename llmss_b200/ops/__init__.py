@@ -15,7 +15,7 @@ import torch
 
 from . import reference as ref
 from .reference import (DECAY_HEAD, DECAY_TOKEN_CHANNEL, DECAY_TOKEN_HEAD, GATE_NONE, GATE_SIGMOID, GATE_SILU, UNARY_NEG_EXP,
-                        UNARY_TANH, distance_bias_table, window_bias_table)
+                        UNARY_TANH, distance_bias_table, rotary_frequencies, window_bias_table)
 from .reference import (ACT_GELU_ERF, ACT_GELU_TANH, ACT_IDS, ACT_NONE, ACT_RELU, ACT_RELU2, ACT_SILU, NORM_DYT, NORM_LAYER,
                         NORM_RMS, ROPE_GPTJ, ROPE_NEOX, ROPE_NONE)
 
@@ -178,15 +178,18 @@ def _sdpa_prefill(qkv, out_view, batch, hq, hkv, d, scale, q_off, k_off, v_off):
         out_view[a:b] = o.transpose(1, 2).reshape(b - a, hq * d)
 
 
-def embed(tokens, wte, positions=None, wpe=None, pos_offset: int = 0, out_dtype=None):
-    """``out_dtype=torch.float32``: rows summed and stored in 32-bit (32-bit residual stream)."""
+def embed(tokens, wte, positions=None, wpe=None, pos_offset: int = 0, out_dtype=None, scale: float = 1.0, out=None):
+    """``out_dtype=torch.float32``: rows summed and stored in 32-bit (32-bit residual stream); then ``scale`` multiplies the
+    token row and ``out`` ([T, width] 32-bit, e.g. a plane of a layer-output history) receives the result."""
     if _cuda(wte):
         from . import cuda_impl as cu
 
         if out_dtype == torch.float32:
-            return cu.embed_f32(tokens, wte, positions, wpe, pos_offset)
+            return cu.embed_f32(tokens, wte, positions, wpe, pos_offset, scale, out)
+        assert scale == 1.0 and out is None, "embed: scale / out belong to the 32-bit form"
         return cu.embed(tokens, wte, positions, wpe, pos_offset)
-    return ref.embed(tokens, wte, positions, wpe, pos_offset, out_dtype=out_dtype)
+    h = ref.embed(tokens, wte, positions, wpe, pos_offset, out_dtype=out_dtype, scale=scale)
+    return h if out is None else out.copy_(h)
 
 
 # ----------------------------------------------------------------------------- 32-bit residual stream, Dynamic Tanh
@@ -220,12 +223,14 @@ def latent_prep(y, q_off, c_off, g_off, n_q, rank, heads, norm_w, eps, slot_mapp
     return ref.latent_prep(y, q_off, c_off, g_off, n_q, rank, heads, norm_w, eps, slot_mapping, cache, dtype)
 
 
-def heads_matmul(x, w, heads, k, n, w_is_kn, row_scale=None, out_dtype=None):
+def heads_matmul(x, w, heads, k, n, w_is_kn, row_scale=None, out_dtype=None, x_head_stride=None, elem_scale=None, out=None,
+                 out_head_stride=None):
+    """Per-head product [T, heads * k] x [heads, k, n]; see ops.reference.heads_matmul for the strides and scales."""
     if _cuda(x):
         from . import cuda_impl as cu
 
-        return cu.heads_matmul(x, w, heads, k, n, w_is_kn, row_scale, out_dtype)
-    return ref.heads_matmul(x, w, heads, k, n, w_is_kn, row_scale, out_dtype)
+        return cu.heads_matmul(x, w, heads, k, n, w_is_kn, row_scale, out_dtype, x_head_stride, elem_scale, out, out_head_stride)
+    return ref.heads_matmul(x, w, heads, k, n, w_is_kn, row_scale, out_dtype, x_head_stride, elem_scale, out, out_head_stride)
 
 
 def latent_query_dtype(cache, heads, rank):
@@ -253,12 +258,13 @@ def latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype):
 
 
 # ----------------------------------------------------------------------------- routed experts
-def moe_route(z, experts, top, groups, keep, route_scale):
+def moe_route(z, experts, top, groups, keep, route_scale, score="softmax", correction=None, group_top=1, renorm=True):
     if _cuda(z):
         from . import cuda_impl as cu
 
-        return cu.moe_route(z, experts, top, groups, keep, route_scale)
-    return ref.moe_route(z, experts, top, groups, keep, route_scale)
+        return cu.moe_route(z, experts, top, groups, keep, route_scale, score=score, correction=correction, group_top=group_top,
+                            renorm=renorm)
+    return ref.moe_route(z, experts, top, groups, keep, route_scale, score, correction, group_top, renorm)
 
 
 def moe_experts(h, ids, wts, w_up, w_down, act, gated: bool = False):
@@ -293,8 +299,8 @@ def token_shift(x, mu, batch, prev_state, out_dtype=None):
     return _dispatch("token_shift", x, x, mu, batch, prev_state, out_dtype)
 
 
-def causal_conv(u, w, bias, act, batch, state):
-    return _dispatch("causal_conv", u, u, w, bias, act, batch, state)
+def causal_conv(u, w, bias, act, batch, state, out_dtype=None):
+    return _dispatch("causal_conv", u, u, w, bias, act, batch, state, out_dtype)
 
 
 def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, positions, slot_mapping, k_cache, v_cache,
@@ -306,17 +312,18 @@ def qknorm_kv_write(qkv, hq, hkv, dk, dv, q_w, k_w, eps, temp_coef, temp_every, 
 
 
 def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None,
-                   window=0, slopes=None):
+                   window=0, slopes=None, sinks=None):
     """Causal paged attention with separate key / value sizes, a per-head distance bias (a table, and / or a linear
-    penalty ``slopes[h] * distance``), an optional sliding window and an output gate.
+    penalty ``slopes[h] * distance``), an optional sliding window, an output gate and an attention sink per head
+    (``sinks`` [hq] 32-bit: exp(sinks[h]) joins every softmax denominator of head h).
     ``bias_over_scale``: dist_bias / scale, kept by the caller for the tensor-core kernels (derived per call if absent)."""
     if _cuda(q):
         from . import cuda_impl as cu
 
         return cu.attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate, out_dtype, bias_over_scale,
-                                 window, slopes)
+                                 window, slopes, sinks)
     return ref.attention_bias(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, batch.cu_q, hq, hkv, dk, dv, scale,
-                              dist_bias, gate, out_dtype, window, slopes)
+                              dist_bias, gate, out_dtype, window, slopes, sinks)
 
 
 def unary(x, op, out_dtype=None):
@@ -354,6 +361,45 @@ def delta_scan(q, k, v, log_decay, beta, batch, state, heads, qk_heads, dk, dv, 
     """Gated delta rule (decay, error-correcting write, read-out after the write); see ops.reference.delta_scan."""
     return _dispatch("delta_scan", v, q, k, v, log_decay, beta, batch, state, heads, qk_heads, dk, dv, unit_eps, q_scale,
                      beta_sigmoid)
+
+
+# ----------------------------------------------------------------------------- rotation by a table, sandwich norms
+def rope_norm_kv_write(qk, hq, hkv, d, freq, mag, interleaved, unit_norm, eps, positions, slot_mapping, k_cache, v_cache,
+                       out_dtype=None):
+    """Rotation of q and k by a frequency table, optional unit RMS per head, keys to the K pages and the projected keys
+    themselves to the V pages; see ops.reference.rope_norm_kv_write."""
+    return _dispatch("rope_norm_kv_write", qk, qk, hq, hkv, d, freq, mag, interleaved, unit_norm, eps, positions, slot_mapping,
+                     k_cache, v_cache, out_dtype)
+
+
+def latent_rope_prep(y, q_off, q_rank, c_off, rank, rot, g_off, n_gate, qn_w, cn_w, eps, freq, mag, positions, slot_mapping, cache,
+                     dtype):
+    """Normed query latent, normed key / value latent + rotated key part into the cache row, sigmoid gate columns."""
+    return _dispatch("latent_rope_prep", y, y, q_off, q_rank, c_off, rank, rot, g_off, n_gate, qn_w, cn_w, eps, freq, mag, positions,
+                     slot_mapping, cache, dtype)
+
+
+def latent_query_rope(q, heads, d, rot, rank, width, freq, mag, positions, dtype, abs_dtype):
+    """Split the up-projected queries into the unrotated operand of the absorption and the rotated part, placed in the
+    absorbed-query buffer."""
+    return _dispatch("latent_query_rope", q, q, heads, d, rot, rank, width, freq, mag, positions, dtype, abs_dtype)
+
+
+def hgrn_gates(y, n_qk, lower):
+    """(silu(q), 1 - f, ln f) with f = lower + (1 - lower) sigmoid(f_raw), from the stacked 32-bit projection [q | f | ...]."""
+    return _dispatch("hgrn_gates", y, y, n_qk, lower)
+
+
+def sandwich_residual(resid, y, w_post, eps, w_next=None, history=None, index=0, depth_w=None, out_dtype=None):
+    """r = resid + rms_div(y) * w_post, optionally stored as layer output ``index`` of ``history`` and replaced by the
+    depth-weighted average of the outputs so far, then h = rms_div(r) * w_next; returns (h, r).  The counterpart of
+    norm_residual / postnorm_residual for sub-layers with a norm on both sides."""
+    return _dispatch("sandwich_residual", resid, resid, y, w_post, eps, w_next, history, index, depth_w, out_dtype)
+
+
+def softcap(z, cap):
+    """cap * tanh(z / cap) in place."""
+    return _dispatch("softcap", z, z, cap)
 
 
 def sample(logits, greedy, temperature, top_k, top_p, rng_state, vocab: Optional[int] = None, out=None):

@@ -156,12 +156,15 @@ def attention_paged(q, k_cache, v_cache, block_tables, seq_lens, cu_q, scale: fl
     return out.to(q.dtype)
 
 
-def embed(tokens, wte, positions=None, wpe=None, pos_offset: int = 0, out_dtype=None):
+def embed(tokens, wte, positions=None, wpe=None, pos_offset: int = 0, out_dtype=None, scale: float = 1.0):
     """Token (+ learned position) embedding (G1; replicated tables, no collective).  With a 32-bit ``out_dtype``
-    the two rows are summed in 32-bit (models that keep their residual stream in 32-bit)."""
+    the two rows are summed in 32-bit (models that keep their residual stream in 32-bit).  ``scale`` multiplies the
+    token row (32-bit output only)."""
     od = out_dtype or wte.dtype
     up = torch.float32 if od == torch.float32 else wte.dtype
     h = F.embedding(tokens.long(), wte).to(up)
+    if scale != 1.0:
+        h = h * scale
     if wpe is not None:
         h = h + F.embedding(positions.long() + pos_offset, wpe).to(up)
     return h.to(od)
@@ -202,15 +205,24 @@ def latent_prep(y, q_off: int, c_off: int, g_off: int, n_q: int, rank: int, head
     return q, gate
 
 
-def heads_matmul(x, w, heads: int, k: int, n: int, w_is_kn: bool, row_scale=None, out_dtype=None):
+def heads_matmul(x, w, heads: int, k: int, n: int, w_is_kn: bool, row_scale=None, out_dtype=None, x_head_stride=None,
+                 elem_scale=None, out=None, out_head_stride=None):
     """Per-head product.  x: [T, heads * k]; w: [heads * k, n] (``w_is_kn``: rows index (head, k)) or [heads * n, k]
-    (rows index (head, n)).  Returns [T, heads * n], optionally scaled per (token, head) by row_scale [T, heads]."""
+    (rows index (head, n)).  Returns [T, heads * n], optionally scaled per (token, head) by row_scale [T, heads] or per
+    element by elem_scale [T, heads * n].  ``x_head_stride`` > k: head h reads x[:, h * stride : h * stride + k];
+    ``out`` / ``out_head_stride``: head h writes out[:, h * stride : h * stride + n] of a given tensor."""
     T = x.shape[0]
-    xh = x.float().view(T, heads, k)
+    xs = x_head_stride or k
+    xh = x.float().reshape(T, heads, xs)[:, :, :k]
     wh = w.float().view(heads, k, n) if w_is_kn else w.float().view(heads, n, k).transpose(1, 2)
     o = torch.einsum("thk,hkn->thn", xh, wh)
     if row_scale is not None:
         o = o * row_scale.float()[:, :, None]
+    if elem_scale is not None:
+        o = o * elem_scale.float().reshape(T, heads, n)
+    if out is not None:
+        out.view(T, heads, out_head_stride or n)[:, :, :n] = o.to(out.dtype)
+        return out
     return o.reshape(T, heads * n).to(out_dtype or x.dtype)
 
 
@@ -238,19 +250,28 @@ def latent_attention(q_abs, cache, block_tables, seq_lens, cu_q, heads: int, ran
 
 
 # ----------------------------------------------------------------------------- routed experts
-def moe_route(z, experts: int, top: int, groups: int, keep: int, route_scale: float):
+def moe_route(z, experts: int, top: int, groups: int, keep: int, route_scale: float, score: str = "softmax", correction=None,
+              group_top: int = 1, renorm: bool = True):
     """Group-limited top-k routing on 32-bit logits z [T, experts] -> (ids [T, top] int32, weights [T, top] fp32).
-    Ties go to the lower index (stable sort), like the CUDA kernel."""
-    s = torch.softmax(z.float(), dim=-1)
+    Scores s = softmax(z) or sigmoid(z) (``score``); experts are *chosen* by s + correction (``correction`` [experts], or
+    none) while the weights are the chosen experts' s.  A group of neighbouring experts scores as the sum of its
+    ``group_top`` largest choice scores (1: its best expert); only experts of the best ``keep`` groups are eligible (the
+    others count as minus infinity: choice scores may be negative).  ``renorm``: weights / (their sum + 1e-20); both forms
+    times ``route_scale``.  Ties go to the lower index (stable sort), like the CUDA kernel."""
+    zf = z.float()
+    s = torch.softmax(zf, dim=-1) if score == "softmax" else torch.sigmoid(zf)
+    c = s if correction is None else s + correction.float()
     T = s.shape[0]
-    gs = s.view(T, groups, experts // groups).amax(-1)
+    per = experts // groups
+    gs = torch.sort(c.view(T, groups, per), dim=-1, descending=True, stable=True).values[:, :, :min(group_top, per)].sum(-1)
     best = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :keep]
     allow = torch.zeros(T, groups, dtype=torch.bool, device=z.device).scatter_(1, best, True)
-    allow = allow[:, :, None].expand(T, groups, experts // groups).reshape(T, experts)
-    idx = torch.sort(s.masked_fill(~allow, -1.0), dim=-1, descending=True, stable=True).indices[:, :top]
+    allow = allow[:, :, None].expand(T, groups, per).reshape(T, experts)
+    idx = torch.sort(c.masked_fill(~allow, float("-inf")), dim=-1, descending=True, stable=True).indices[:, :top]
     w = s.gather(1, idx)
-    w = w / (w.sum(-1, keepdim=True) + 1e-20) * route_scale
-    return idx.to(torch.int32), w
+    if renorm:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return idx.to(torch.int32), w * route_scale
 
 
 def moe_experts(h, ids, wts, w_up, w_down, act: int, gated: bool = False):
@@ -499,10 +520,10 @@ def token_shift(x, mu, batch, prev_state, out_dtype=None):
     return out.to(out_dtype or x.dtype)
 
 
-def causal_conv(u, w, bias, act: int, batch, state):
+def causal_conv(u, w, bias, act: int, batch, state, out_dtype=None):
     """Short causal convolution over time per channel: y_t = sum_j w[:, j] u_(t - taps + 1 + j) (+ bias), then ``act``.
     u [T, C] (a column view is fine), w [C, taps]; ``state`` [slots, taps - 1, C] 32-bit holds each sequence's last
-    taps - 1 inputs (zeros before its start).  32-bit result."""
+    taps - 1 inputs (zeros before its start).  32-bit arithmetic; the result is 32-bit unless ``out_dtype`` says otherwise."""
     T, C = u.shape
     taps = w.shape[1]
     wf, uf = w.float(), u.float()
@@ -516,7 +537,7 @@ def causal_conv(u, w, bias, act: int, batch, state):
             state[slot] = full[full.shape[0] - (taps - 1):]
     if bias is not None:
         y = y + bias.float()
-    return apply_act(y, act)
+    return apply_act(y, act).to(out_dtype or torch.float32)
 
 
 def qknorm_kv_write(qkv, hq: int, hkv: int, dk: int, dv: int, q_w, k_w, eps: float, temp_coef: float, temp_every: int,
@@ -591,7 +612,7 @@ def window_bias_table(slopes, window: int, scale: float):
 
 
 def attention_bias(q, k_cache, v_cache, block_tables, seq_lens, cu_q, hq: int, hkv: int, dk: int, dv: int, scale: float,
-                   dist_bias, gate=None, out_dtype=None, window: int = 0, slopes=None):
+                   dist_bias, gate=None, out_dtype=None, window: int = 0, slopes=None, sinks=None):
     """Causal softmax attention over the paged cache with key size dk, value size dv, grouped heads, an additive bias
     dist_bias[h, min(i - j, last)] per head and distance (or none), a linear penalty slopes[h] * (i - j) taken off the
     scores (or none), a sliding window (``window`` > 0: query i sees keys j with 0 <= i - j < window), and an optional
@@ -622,7 +643,11 @@ def attention_bias(q, k_cache, v_cache, block_tables, seq_lens, cu_q, hq: int, h
         if window > 0:
             hidden = hidden | (qpos - kpos >= window)
         s = s.masked_fill(hidden, float("-inf"))
-        out[q0:q1] = torch.matmul(torch.softmax(s, dim=-1), v).permute(1, 0, 2)
+        if sinks is not None:
+            p = torch.softmax(torch.cat([s, sinks.float().view(hq, 1, 1).expand(hq, ql, 1)], dim=-1), dim=-1)[..., :L]
+        else:
+            p = torch.softmax(s, dim=-1)
+        out[q0:q1] = torch.matmul(p, v).permute(1, 0, 2)
     if gate is not None:
         out = out * torch.sigmoid(gate.float())[:, :, None]
     return out.reshape(T, hq * dv).to(out_dtype or q.dtype)
@@ -760,3 +785,136 @@ def delta_scan(q, k, v, log_decay, beta, batch, state, heads: int, qk_heads: int
             out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
         state[slot] = S
     return out.reshape(T, heads * dv)
+
+
+# ----------------------------------------------------------------------------- rotation by a frequency table, sandwich norms
+def rotary_frequencies(dims: int, base: float, scaling=None):
+    """Frequencies of a rotary position embedding over ``dims`` channels as a table, plus the factor on cos and sin:
+    (f [dims / 2] float64, magnitude).  f_i = base^(-2 i / dims); ``scaling`` = {"factor"} divides every frequency (linear
+    position interpolation); {"factor", "original", "fast", "slow"} blends per frequency (YaRN): with
+    dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1)
+    and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i) and
+    the magnitude 0.1 ln(factor) + 1.  The kernels take the table, so any other schedule is a different table."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    if not scaling:
+        return f, 1.0
+    factor = float(scaling["factor"])
+    if "original" not in scaling:
+        return f / factor, 1.0
+    orig, fast, slow = float(scaling["original"]), float(scaling["fast"]), float(scaling["slow"])
+
+    def at(t):
+        return dims * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+
+    lo, hi = max(math.floor(at(fast)), 0), min(math.ceil(at(slow)), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+def _rotate_by_table(x, positions, freq, mag: float, interleaved: bool):
+    """x [T, heads, d] 32-bit: the first 2 * len(freq) channels of every head are rotated (angles in 64-bit), the rest pass."""
+    n = freq.numel()
+    if n == 0:
+        return x
+    ang = positions.double()[:, None] * freq.double().to(x.device)[None, :]
+    c, s = (torch.cos(ang) * mag).float()[:, None, :], (torch.sin(ang) * mag).float()[:, None, :]
+    part, rest = x[..., :2 * n], x[..., 2 * n:]
+    if interleaved:
+        u, v = part[..., 0::2], part[..., 1::2]
+        out = torch.stack((u * c - v * s, v * c + u * s), dim=-1).flatten(-2)
+    else:
+        u, v = part[..., :n], part[..., n:]
+        out = torch.cat((u * c - v * s, v * c + u * s), dim=-1)
+    return torch.cat((out, rest), dim=-1)
+
+
+def rope_norm_kv_write(qk, hq: int, hkv: int, d: int, freq, mag: float, interleaved: bool, unit_norm: bool, eps: float,
+                       positions, slot_mapping, k_cache, v_cache, out_dtype=None):
+    """Queries and keys of grouped-query attention whose values are the keys as projected.  qk [T, hq*d + hkv*d] 32-bit.
+    q and k are rotated by the frequency table (pairs (2i, 2i+1) if ``interleaved`` else (i, i + n)), then -- ``unit_norm``
+    -- every head is divided by its root mean square (no weight).  The prepared keys go to the K pages, the projected
+    keys themselves (before rotation and norm) to the V pages.  Returns the queries [T, hq * d]."""
+    T = qk.shape[0]
+    q = qk[:, :hq * d].float().view(T, hq, d)
+    k = qk[:, hq * d:(hq + hkv) * d].float().view(T, hkv, d)
+    qr, kr = _rotate_by_table(q, positions, freq, mag, interleaved), _rotate_by_table(k, positions, freq, mag, interleaved)
+    if unit_norm:
+        qr, kr = _rms_div(qr, eps), _rms_div(kr, eps)
+    bs = k_cache.shape[2]
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    k_cache[slots // bs, :, slots % bs, :] = kr[valid].to(k_cache.dtype)
+    v_cache[slots // bs, :, slots % bs, :] = k[valid].to(v_cache.dtype)
+    return qr.reshape(T, hq * d).to(out_dtype or k_cache.dtype)
+
+
+def latent_rope_prep(y, q_off: int, q_rank: int, c_off: int, rank: int, rot: int, g_off: int, n_gate: int, qn_w, cn_w, eps: float,
+                     freq, mag: float, positions, slot_mapping, cache, dtype):
+    """First stage of latent attention with a rotated key part, on the layer's fused 32-bit projection y [T, *]:
+    the query latent y[:, q_off : q_off + q_rank] is RMS-normed (weight ``qn_w``) and returned in ``dtype`` (the operand of the
+    query up-projection; q_rank = 0: there is none); the key / value latent y[:, c_off : c_off + rank] is RMS-normed
+    (weight ``cn_w``), the ``rot`` columns behind it are rotated (interleaved pairs) and not normed, and both are written
+    side by side into the token's cache row (cache [num_blocks, block_size, >= rank + rot]; columns beyond are zeroed);
+    sigmoid of the n_gate gate columns is returned in 32-bit ([T, n_gate], or None)."""
+    T = y.shape[0]
+    cq = None
+    if q_rank > 0:
+        cq = (_rms_div(y[:, q_off:q_off + q_rank].float(), eps) * qn_w.float()).to(dtype)
+    c = _rms_div(y[:, c_off:c_off + rank].float(), eps) * cn_w.float()
+    kr = _rotate_by_table(y[:, c_off + rank:c_off + rank + rot].float().reshape(T, 1, rot), positions, freq, mag, True).reshape(T, rot)
+    width = cache.shape[-1]
+    row = torch.zeros(T, width, dtype=torch.float32, device=y.device)
+    row[:, :rank], row[:, rank:rank + rot] = c, kr
+    valid = slot_mapping >= 0
+    cache.view(-1, width)[slot_mapping[valid].long()] = row[valid].to(cache.dtype)
+    gate = torch.sigmoid(y[:, g_off:g_off + n_gate].float()) if n_gate > 0 else None
+    return cq, gate
+
+
+def latent_query_rope(q, heads: int, d: int, rot: int, rank: int, width: int, freq, mag: float, positions, dtype, abs_dtype):
+    """Second stage: q [T, heads * (d + rot)] (every head [d unrotated | rot rotated]).  Returns (q_nope [T, heads * d] in
+    ``dtype`` -- the operand of the per-head key absorption -- and the absorbed-query buffer [T, heads * width] in
+    ``abs_dtype`` whose columns [rank, rank + rot) of every head hold the rotated part (interleaved pairs); columns below
+    ``rank`` are left for the absorption product, columns beyond rank + rot are zero."""
+    T = q.shape[0]
+    qh = q.float().view(T, heads, d + rot)
+    qa = torch.zeros(T, heads, width, dtype=abs_dtype, device=q.device)
+    qa[:, :, rank:rank + rot] = _rotate_by_table(qh[..., d:], positions, freq, mag, True).to(abs_dtype)
+    return qh[..., :d].reshape(T, heads * d).to(dtype), qa.view(T, heads * width)
+
+
+def hgrn_gates(y, n_qk: int, lower):
+    """Inputs of a gated linear recurrence whose forget gate also decides what is written, from y [T, 2 n_qk + *] 32-bit
+    = [q | f | ...]: q <- silu(q); f = lower + (1 - lower) sigmoid(f); returns (q, k = 1 - f, ln f), each [T, n_qk] 32-bit.
+    1 - f is formed as (1 - lower) sigmoid(-f_raw), without cancellation."""
+    q = F.silu(y[:, :n_qk].float())
+    z = y[:, n_qk:2 * n_qk].float()
+    lo = lower.float()
+    f = lo + (1.0 - lo) * torch.sigmoid(z)
+    k = (1.0 - lo) * torch.sigmoid(-z)
+    return q, k, torch.log(f)
+
+
+def sandwich_residual(resid, y, w_post, eps: float, w_next=None, history=None, index: int = 0, depth_w=None, out_dtype=None):
+    """Residual update of a sub-layer that is normed on both sides, fused with the norm in front of the next one:
+         r = resid + rms_div(y) * w_post                                (y None: r = resid)
+         history given:  history[index] = r ;  r = sum_(j <= index) depth_w[j] * history[j]     (depth-weighted average)
+         h = rms_div(r) * w_next                                        (w_next None: no h)
+    resid [T, W] 32-bit, y [T, W] 32-bit, history [n, T, W] 32-bit.  Returns (h in ``out_dtype`` or None, r 32-bit)."""
+    r = resid.float()
+    if y is not None:
+        r = r + _rms_div(y.float(), eps) * w_post.float()
+    if history is not None:
+        history[index] = r
+        if depth_w is not None:
+            r = torch.einsum("j,jtw->tw", depth_w.float()[:index + 1], history[:index + 1])
+    h = None
+    if w_next is not None:
+        h = (_rms_div(r, eps) * w_next.float()).to(out_dtype or torch.float32)
+    return h, r
+
+
+def softcap(z, cap: float):
+    """cap * tanh(z / cap), in place on 32-bit logits."""
+    return z.copy_(cap * torch.tanh(z.float() / cap))
