@@ -132,6 +132,7 @@ struct AbArgs {
   const float* slopes;                    // [hq] linear distance penalty, or null
   int window;                             // > 0: only keys with i - j < window are visible
   const float* gate; int64_t ldg;         // [T][hq] logits, or null
+  const float* sinks;                     // [hq] sink logits (one more term exp(sinks[h]) in every denominator), or null
   void* out;                              // [T][hq * dv]
   int hq, hkv, dk, dv, nh, rows, hsub;    // nh: query heads per CTA; rows: query rows per CTA; hsub: CTAs per kv head
   float scale;
@@ -220,6 +221,12 @@ __global__ void __launch_bounds__(NW * 32) attention_bias_kernel(AbArgs a) {
   }
   if (!active) return;
   float gsc = 1.f / l;
+  if (a.sinks != nullptr) {       // the sink has no key and no value: it only enlarges the denominator
+    const float sk = a.sinks[h];
+    const float mn = fmaxf(m, sk);
+    const float corr = expf(m - mn);
+    gsc = corr / (l * corr + expf(sk - mn));
+  }
   if (a.gate != nullptr) gsc *= 1.f / (1.f + expf(-a.gate[(int64_t)(q0 + row) * a.ldg + h]));
   T* og = reinterpret_cast<T*>(a.out) + (int64_t)(q0 + row) * a.hq * dv + (int64_t)h * dv;
 #pragma unroll
@@ -277,7 +284,8 @@ LLMSS_API int llmss_head_gate(void* x, int64_t ldx, const float* gate, int64_t l
 static int attention_bias_launch(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                                  int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias,
                                  int n_dist, const float* slopes, int window, const float* gate, int64_t ldg, void* out, int B,
-                                 int max_q, int hq, int hkv, int dk, int dv, float scale, int dtype, cudaStream_t stream) {
+                                 int max_q, int hq, int hkv, int dk, int dv, float scale, int dtype, cudaStream_t stream,
+                                 const float* sinks = nullptr) {
   LLMSS_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_bias: %d query heads over %d key/value heads", hq, hkv);
   LLMSS_REQUIRE(dv <= 32 * MAXV, "attention_bias: value size %d (at most %d)", dv, 32 * MAXV);
   LLMSS_REQUIRE(bias == nullptr || n_dist > 0, "attention_bias: empty bias table");
@@ -285,6 +293,7 @@ static int attention_bias_launch(const void* q, int64_t ldq, const void* k_cache
   AbArgs a;
   a.q = q; a.ldq = ldq; a.k_cache = k_cache; a.v_cache = v_cache; a.block_tables = block_tables; a.max_blocks = max_blocks;
   a.bs = block_size; a.seq_lens = seq_lens; a.cu_q = cu_q; a.bias = bias; a.n_dist = n_dist; a.slopes = slopes; a.window = window; a.gate = gate; a.ldg = ldg; a.out = out;
+  a.sinks = sinks;
   a.hq = hq; a.hkv = hkv; a.dk = dk; a.dv = dv; a.scale = scale;
   const int gsz = hq / hkv;
   a.nh = gsz < NW ? gsz : NW;
@@ -325,4 +334,15 @@ LLMSS_API int llmss_attention_window(const void* q, int64_t ldq, const void* k_c
   LLMSS_REQUIRE(window >= 0, "attention_window: window %d", window);
   return attention_bias_launch(q, ldq, k_cache, v_cache, block_tables, max_blocks, block_size, seq_lens, cu_q, bias, n_dist, slopes,
                                window, gate, ldg, out, B, max_q, hq, hkv, dk, dv, scale, dtype, stream);
+}
+
+// the same with an attention sink per head (sinks [hq] or null): exp(sinks[h]) joins every softmax denominator of head h
+LLMSS_API int llmss_attention_sink(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                                   int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias,
+                                   int n_dist, const float* slopes, int window, const float* gate, int64_t ldg, const float* sinks,
+                                   void* out, int B, int max_q, int hq, int hkv, int dk, int dv, float scale, int dtype,
+                                   cudaStream_t stream) {
+  LLMSS_REQUIRE(window >= 0, "attention_sink: window %d", window);
+  return attention_bias_launch(q, ldq, k_cache, v_cache, block_tables, max_blocks, block_size, seq_lens, cu_q, bias, n_dist, slopes,
+                               window, gate, ldg, out, B, max_q, hq, hkv, dk, dv, scale, dtype, stream, sinks);
 }

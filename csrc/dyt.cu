@@ -34,14 +34,14 @@ template <typename T>
 __global__ void __launch_bounds__(128) embed_f32_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                                                         const T* __restrict__ wte, const T* __restrict__ wpe,
                                                         float* __restrict__ out, int H, int vocab, int max_pos,
-                                                        int pos_offset, int64_t ldo) {
+                                                        int pos_offset, int64_t ldo, float scale) {
   const int t = blockIdx.x;
   const int tok = min(max(tokens[t], 0), vocab - 1);
   const T* src = wte + (int64_t)tok * H;
   const T* psrc = nullptr;
   if (wpe != nullptr) psrc = wpe + (int64_t)min(max(positions[t] + pos_offset, 0), max_pos - 1) * H;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float v = to_f32(src[c]);
+    float v = to_f32(src[c]) * scale;
     if (psrc != nullptr) v += to_f32(psrc[c]);
     out[(int64_t)t * ldo + c] = v;
   }
@@ -71,13 +71,20 @@ LLMSS_API int llmss_dyt_residual(const float* res_in, float* res_out, const floa
   return 0;
 }
 
-LLMSS_API int llmss_embed_f32(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int T_,
-                              int H, int vocab, int max_pos, int pos_offset, int64_t ldo, int dtype, cudaStream_t stream) {
+// out[t] = wte[tok_t] * scale (+ wpe[pos_t]) in 32-bit
+LLMSS_API int llmss_embed_scaled_f32(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int T_,
+                                     int H, int vocab, int max_pos, int pos_offset, int64_t ldo, float scale, int dtype,
+                                     cudaStream_t stream) {
   if (T_ == 0) return 0;
   LLMSS_BY_DTYPE(dtype, (embed_f32_kernel<T><<<T_, 128, 0, stream>>>(tokens, positions, (const T*)wte, (const T*)wpe, out, H,
-                                                                    vocab, max_pos, pos_offset, ldo)));
+                                                                    vocab, max_pos, pos_offset, ldo, scale)));
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+LLMSS_API int llmss_embed_f32(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int T_,
+                              int H, int vocab, int max_pos, int pos_offset, int64_t ldo, int dtype, cudaStream_t stream) {
+  return llmss_embed_scaled_f32(tokens, positions, wte, wpe, out, T_, H, vocab, max_pos, pos_offset, ldo, 1.f, dtype, stream);
 }
 
 LLMSS_API int llmss_cast_concat(const float* a, const float* b, void* out, int M, int Ha, int Hb, int64_t lda, int64_t ldb,

@@ -1,9 +1,10 @@
 // Routed mixture of experts: grouped top-k router and the per-token expert products.
 //
-//   moe_route : scores s = softmax(z) over all E experts (32-bit); the experts form `groups` equal groups of
-//               neighbours, a group scores as its best expert, only experts of the `keep` best groups are eligible;
-//               the `top` eligible experts with the largest scores are chosen; weights = s_chosen / (sum + 1e-20)
-//               * route_scale.  Ties go to the lower index.  One warp per token.
+//   moe_route : scores s = softmax(z) or sigmoid(z) over all E experts (32-bit); experts are chosen by s plus an optional
+//               per-expert correction, weighted by s itself; the experts form `groups` equal groups of neighbours, a
+//               group scores as its best expert (or as the sum of its few best), only experts of the `keep` best groups
+//               are eligible; the `top` eligible experts with the largest choice scores are chosen; weights = s_chosen
+//               (/ (sum + 1e-20) if renormalised) * route_scale.  Ties go to the lower index.  One warp per token.
 //   moe_up    : a[t, k, :] = act(W_up[e_k] h_t)            one warp per output feature, weights read row-wise
 //   moe_down  : y[t, :]    = sum_k w_k W_down[e_k] a[t, k] 32-bit output; the experts' down matrices lie side by side
 //               in one [W, E * F] tensor (row stride ldd), which is also the dense form's GEMM operand
@@ -16,14 +17,23 @@ namespace {
 
 constexpr int kMaxPerLane = 8;   // experts per lane: E <= 256
 
+constexpr int kMaxGroupTop = 4;  // a group scores as the sum of at most this many of its best experts
+
+// score_kind 0: s = softmax(z); 1: s = sigmoid(z).  Experts are chosen by c = s + correction (correction may be null); the
+// weights are the chosen experts' s.  A group scores as the sum of its `group_top` largest c (1: its best expert).
+// renorm: weights / (their sum + 1e-20).  Experts outside the kept groups are never chosen, whatever the sign of c.
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int64_t ldz, int E, int top, int groups,
-                                                        int keep, float route_scale, int* __restrict__ ids,
-                                                        float* __restrict__ wts, float* __restrict__ dense, int T) {
+                                                        int keep, float route_scale, int score_kind,
+                                                        const float* __restrict__ correction, int group_top, int renorm,
+                                                        int* __restrict__ ids, float* __restrict__ wts,
+                                                        float* __restrict__ dense, int T) {
+  __shared__ float cs_all[4][32 * kMaxPerLane];
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
+  float* cs = cs_all[threadIdx.x >> 5];
   const float* zr = z + (int64_t)t * ldz;
-  float s[kMaxPerLane];
+  float s[kMaxPerLane], c[kMaxPerLane];
   bool ok[kMaxPerLane];
   float mx = -INFINITY;
 #pragma unroll
@@ -32,37 +42,71 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     s[i] = e < E ? zr[e] : -INFINITY;
     mx = fmaxf(mx, s[i]);
   }
-  mx = warp_max(mx);
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
-    const int e = lane + i * 32;
-    s[i] = e < E ? expf(s[i] - mx) : 0.f;
-    sum += s[i];
-  }
-  sum = warp_sum(sum);
-#pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) { s[i] /= sum; ok[i] = false; }
-  // best `keep` groups: repeatedly take the group with the largest (best expert) score
-  const int gsz = E / groups;
-  unsigned long long taken_lo = 0ull, taken_hi = 0ull, taken_2 = 0ull, taken_3 = 0ull;   // up to 256 groups
-  for (int n = 0; n < keep; ++n) {
-    float bv = -1.f;
-    int bg = 0x7fffffff;
+  if (score_kind == 0) {
+    mx = warp_max(mx);
+    float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
       const int e = lane + i * 32;
-      if (e >= E) continue;
-      const int g = e / gsz;
+      s[i] = e < E ? expf(s[i] - mx) : 0.f;
+      sum += s[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) s[i] /= sum;
+  } else {
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) s[i] = lane + i * 32 < E ? 1.f / (1.f + expf(-s[i])) : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxPerLane; ++i) {
+    const int e = lane + i * 32;
+    c[i] = e < E ? s[i] + (correction != nullptr ? correction[e] : 0.f) : -INFINITY;
+    ok[i] = false;
+    if (e < E) cs[e] = c[i];
+  }
+  __syncwarp();
+  // group scores: lane l owns groups l, l + 32, ...
+  const int gsz = E / groups;
+  float gs[kMaxPerLane];
+#pragma unroll
+  for (int j = 0; j < kMaxPerLane; ++j) {
+    const int g = lane + j * 32;
+    gs[j] = -INFINITY;
+    if (g >= groups) continue;
+    float best[kMaxGroupTop];
+#pragma unroll
+    for (int n = 0; n < kMaxGroupTop; ++n) best[n] = -INFINITY;
+    for (int e = g * gsz; e < (g + 1) * gsz; ++e) {
+      float v = cs[e];
+#pragma unroll
+      for (int n = 0; n < kMaxGroupTop; ++n)
+        if (n < group_top && v > best[n]) { const float o = best[n]; best[n] = v; v = o; }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int n = 0; n < kMaxGroupTop; ++n)
+      if (n < group_top && n < gsz) sum += best[n];
+    gs[j] = sum;
+  }
+  // best `keep` groups: repeatedly take the group with the largest score (ties: the lower group)
+  unsigned long long taken_lo = 0ull, taken_hi = 0ull, taken_2 = 0ull, taken_3 = 0ull;   // up to 256 groups
+  for (int n = 0; n < keep; ++n) {
+    float bv = -INFINITY;
+    int bg = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int g = lane + j * 32;
+      if (g >= groups) continue;
       const unsigned long long word = g < 64 ? taken_lo : g < 128 ? taken_hi : g < 192 ? taken_2 : taken_3;
       if ((word >> (g & 63)) & 1ull) continue;
-      if (s[i] > bv || (s[i] == bv && g < bg)) { bv = s[i]; bg = g; }
+      if (gs[j] > bv || (gs[j] == bv && g < bg) || bg == 0x7fffffff) { bv = gs[j]; bg = g; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       const int og = __shfl_xor_sync(0xffffffffu, bg, o);
-      if (ov > bv || (ov == bv && og < bg)) { bv = ov; bg = og; }
+      if (og != 0x7fffffff && (bg == 0x7fffffff || ov > bv || (ov == bv && og < bg))) { bv = ov; bg = og; }
     }
     if (bg < 64) taken_lo |= 1ull << bg; else if (bg < 128) taken_hi |= 1ull << (bg - 64);
     else if (bg < 192) taken_2 |= 1ull << (bg - 128); else if (bg < 256) taken_3 |= 1ull << (bg - 192);
@@ -75,31 +119,33 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     const unsigned long long word = g < 64 ? taken_lo : g < 128 ? taken_hi : g < 192 ? taken_2 : taken_3;
     ok[i] = (word >> (g & 63)) & 1ull;
   }
-  // top experts among the eligible ones
+  // top experts among the eligible ones, by choice score; the weight is the plain score
   float wsum = 0.f;
   float myw = 0.f;      // lane n keeps the n-th pick (top <= 32)
   int myid = 0;
+  bool mine = false;
   for (int n = 0; n < top; ++n) {
-    float bv = -1.f;
+    float bv = -INFINITY, bs = 0.f;
     int be = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
       const int e = lane + i * 32;
-      if (e < E && ok[i] && (s[i] > bv || (s[i] == bv && e < be))) { bv = s[i]; be = e; }
+      if (e < E && ok[i] && (be == 0x7fffffff || c[i] > bv || (c[i] == bv && e < be))) { bv = c[i]; be = e; bs = s[i]; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const float os = __shfl_xor_sync(0xffffffffu, bs, o);
       const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+      if (oe != 0x7fffffff && (be == 0x7fffffff || ov > bv || (ov == bv && oe < be))) { bv = ov; be = oe; bs = os; }
     }
     if (be < E) {
       if ((be & 31) == lane) ok[be >> 5] = false;
-      wsum += bv;
-      if (lane == n) { myw = bv; myid = be; }
+      wsum += bs;
+      if (lane == n) { myw = bs; myid = be; mine = true; }
     } else if (lane == n) { myw = 0.f; myid = 0; }
   }
-  const float inv = route_scale / (wsum + 1e-20f);
+  const float inv = renorm ? route_scale / (wsum + 1e-20f) : route_scale;
   if (lane < top) {
     ids[(int64_t)t * top + lane] = myid;
     wts[(int64_t)t * top + lane] = myw * inv;
@@ -107,7 +153,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   if (dense != nullptr) {   // [T, E] routing weights, 0 for experts that were not chosen
     for (int e = lane; e < E; e += 32) dense[(int64_t)t * E + e] = 0.f;
     __syncwarp();
-    if (lane < top && myw > 0.f) dense[(int64_t)t * E + myid] = myw * inv;
+    if (lane < top && mine) dense[(int64_t)t * E + myid] = myw * inv;
   }
 }
 
@@ -261,16 +307,25 @@ int launch_experts(const void* h, int64_t ldh, const int* ids, const float* wts,
 
 }  // namespace
 
-LLMSS_API int llmss_moe_route(const float* z, int64_t ldz, int T_, int E, int top, int groups, int keep, float route_scale,
-                              int* ids, float* wts, float* dense, cudaStream_t stream) {
+LLMSS_API int llmss_moe_route_ex(const float* z, int64_t ldz, int T_, int E, int top, int groups, int keep, float route_scale,
+                                 int score_kind, const float* correction, int group_top, int renorm, int* ids, float* wts,
+                                 float* dense, cudaStream_t stream) {
   LLMSS_REQUIRE(E > 0 && E <= 32 * kMaxPerLane, "moe_route: %d experts (at most %d)", E, 32 * kMaxPerLane);
   LLMSS_REQUIRE(top > 0 && top <= 32 && top <= E, "moe_route: top=%d must be in 1..min(32, experts)", top);
   LLMSS_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups, "moe_route: bad groups %d / keep %d for %d experts",
                 groups, keep, E);
+  LLMSS_REQUIRE(score_kind == 0 || score_kind == 1, "moe_route: score kind %d (0 softmax, 1 sigmoid)", score_kind);
+  LLMSS_REQUIRE(group_top >= 1 && group_top <= kMaxGroupTop, "moe_route: a group sums its %d best (1..%d)", group_top, kMaxGroupTop);
   if (T_ == 0) return 0;
-  moe_route_kernel<<<(T_ + 3) / 4, 128, 0, stream>>>(z, ldz, E, top, groups, keep, route_scale, ids, wts, dense, T_);
+  moe_route_kernel<<<(T_ + 3) / 4, 128, 0, stream>>>(z, ldz, E, top, groups, keep, route_scale, score_kind, correction, group_top,
+                                                     renorm, ids, wts, dense, T_);
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+LLMSS_API int llmss_moe_route(const float* z, int64_t ldz, int T_, int E, int top, int groups, int keep, float route_scale,
+                              int* ids, float* wts, float* dense, cudaStream_t stream) {
+  return llmss_moe_route_ex(z, ldz, T_, E, top, groups, keep, route_scale, 0, nullptr, 1, 1, ids, wts, dense, stream);
 }
 
 LLMSS_API int llmss_moe_experts(const void* h, int64_t ldh, const int* ids, const float* wts, const void* w_up,

@@ -165,9 +165,9 @@ constexpr int kConvChunk = 64, kMaxTapsAny = 16;
 
 // grid (B, ceil(C / 128), token chunks); thread = channel; chunk 0 of a sequence reads and replaces the slot's tail.
 // kMaxTaps bounds the register window (instantiated for 4, 8 and 16 taps).
-template <int kMaxTaps>
+template <int kMaxTaps, typename TO>
 __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restrict__ u, int64_t ldu, const float* __restrict__ w,
-                                                          const float* __restrict__ bias, float* __restrict__ out, int C, int taps,
+                                                          const float* __restrict__ bias, TO* __restrict__ out, int C, int taps,
                                                           int act, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                                                           const int* __restrict__ slots, float* __restrict__ state) {
   const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restric
       for (int i = 0; i < kMaxTaps; ++i) if (i < taps) acc = fmaf(wt[i], i < hist ? win[i] : cur, acc);
 #pragma unroll
       for (int i = 0; i < kMaxTaps - 1; ++i) win[i] = i + 1 < hist ? win[i + 1] : cur;
-      out[(int64_t)(s.q0 + j) * C + c] = act_exact(acc, act);
+      out[(int64_t)(s.q0 + j) * C + c] = from_f32<TO>(act_exact(acc, act));
     }
     if (z == 0 && st != nullptr) {
       // new tail: inputs ql - hist .. ql - 1; those before this step's first row come from the old tail
@@ -222,9 +222,16 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restric
 
 // The same with four neighbouring channels per thread: 16-byte loads and stores (C and ldu multiples of 4, 16-byte aligned
 // bases); grid (B, ceil(C / 512), token chunks of CH tokens: shorter chunks than the scalar form, for enough blocks).
-template <int kMaxTaps, int CH>
+template <typename TO> __device__ __forceinline__ void store4(TO* p, float a, float b, float c, float d) {
+  struct alignas(4 * sizeof(TO)) V4 { TO v[4]; };
+  V4 o;
+  o.v[0] = from_f32<TO>(a); o.v[1] = from_f32<TO>(b); o.v[2] = from_f32<TO>(c); o.v[3] = from_f32<TO>(d);
+  *reinterpret_cast<V4*>(p) = o;
+}
+
+template <int kMaxTaps, int CH, typename TO>
 __global__ void __launch_bounds__(128) causal_conv4_kernel(const float* __restrict__ u, int64_t ldu, const float* __restrict__ w,
-                                                           const float* __restrict__ bias, float* __restrict__ out, int C, int taps,
+                                                           const float* __restrict__ bias, TO* __restrict__ out, int C, int taps,
                                                            int act, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                                                            const int* __restrict__ slots, float* __restrict__ state) {
   const Seq s = seq_of(cu_q, seq_lens, slots, blockIdx.x);
@@ -254,7 +261,7 @@ __global__ void __launch_bounds__(128) causal_conv4_kernel(const float* __restri
       win[i] = i >= hist ? zero : (jj >= 0 ? *reinterpret_cast<const float4*>(u + (int64_t)(s.q0 + jj) * ldu + c) : old[i]);
     }
     const float* up = u + (int64_t)(s.q0 + j0) * ldu + c;
-    float* op = out + (int64_t)(s.q0 + j0) * C + c;
+    TO* op = out + (int64_t)(s.q0 + j0) * C + c;
 #pragma unroll 4
     for (int j = j0; j < j1; ++j, up += ldu, op += C) {
       const float4 cur = *reinterpret_cast<const float4*>(up);
@@ -269,7 +276,7 @@ __global__ void __launch_bounds__(128) causal_conv4_kernel(const float* __restri
       }
 #pragma unroll
       for (int i = 0; i < kMaxTaps - 1; ++i) win[i] = i + 1 < hist ? win[i + 1] : cur;
-      *reinterpret_cast<float4*>(op) = make_float4(act_exact(acc.x, act), act_exact(acc.y, act), act_exact(acc.z, act), act_exact(acc.w, act));
+      store4<TO>(op, act_exact(acc.x, act), act_exact(acc.y, act), act_exact(acc.z, act), act_exact(acc.w, act));
     }
     if (z == 0 && st != nullptr) {
       // new tail: inputs ql - hist .. ql - 1; those before this step's first row come from the old tail
@@ -977,27 +984,42 @@ LLMSS_API int llmss_token_shift(const float* x, int64_t ldx, const float* mu, in
   return 0;
 }
 
-LLMSS_API int llmss_causal_conv(const float* u, int64_t ldu, const float* w, const float* bias, float* out, int T_, int C, int taps,
-                                int act, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, float* state,
-                                cudaStream_t stream) {
-  LLMSS_REQUIRE(taps >= 1 && taps <= kMaxTapsAny, "causal_conv: %d taps (1..%d)", taps, kMaxTapsAny);
-  LLMSS_REQUIRE(taps == 1 || state != nullptr, "causal_conv: more than one tap needs a state");
-  if (B <= 0 || T_ <= 0) return 0;
+template <typename TO>
+static int causal_conv_launch(const float* u, int64_t ldu, const float* w, const float* bias, TO* out, int T_, int C, int taps,
+                              int act, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, float* state,
+                              cudaStream_t stream) {
   const int chunks = max(1, min((max_q + kConvChunk - 1) / kConvChunk, 64));
   if (taps <= 4 && C % 4 == 0 && ldu % 4 == 0 &&
       ((((uintptr_t)u) | ((uintptr_t)out) | ((uintptr_t)bias) | ((uintptr_t)state)) & 15) == 0) {
     // (a null bias or state is aligned; the state's rows are C floats apart)
     const dim3 grid4(B, (C / 4 + 127) / 128, max(1, min((max_q + 15) / 16, 128)));
-    causal_conv4_kernel<4, 16><<<grid4, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+    causal_conv4_kernel<4, 16, TO><<<grid4, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
     LLMSS_CHECK_CUDA(cudaGetLastError());
     return 0;
   }
   const dim3 grid(B, (C + 127) / 128, chunks);
-  if (taps <= 4) causal_conv_kernel<4><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
-  else if (taps <= 8) causal_conv_kernel<8><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
-  else causal_conv_kernel<16><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+  if (taps <= 4) causal_conv_kernel<4, TO><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+  else if (taps <= 8) causal_conv_kernel<8, TO><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
+  else causal_conv_kernel<16, TO><<<grid, 128, 0, stream>>>(u, ldu, w, bias, out, C, taps, act, cu_q, seq_lens, slots, state);
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+// out: [T, C] in out_dtype (32-bit, or the 16-bit type of the GEMM that reads it); the arithmetic and the tails are 32-bit
+LLMSS_API int llmss_causal_conv_to(const float* u, int64_t ldu, const float* w, const float* bias, void* out, int out_dtype, int T_,
+                                   int C, int taps, int act, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q,
+                                   float* state, cudaStream_t stream) {
+  LLMSS_REQUIRE(taps >= 1 && taps <= kMaxTapsAny, "causal_conv: %d taps (1..%d)", taps, kMaxTapsAny);
+  LLMSS_REQUIRE(taps == 1 || state != nullptr, "causal_conv: more than one tap needs a state");
+  if (B <= 0 || T_ <= 0) return 0;
+  LLMSS_BY_DTYPE(out_dtype, return (causal_conv_launch<T>(u, ldu, w, bias, (T*)out, T_, C, taps, act, cu_q, seq_lens, slots, B, max_q,
+                                                           state, stream)));
+}
+
+LLMSS_API int llmss_causal_conv(const float* u, int64_t ldu, const float* w, const float* bias, float* out, int T_, int C, int taps,
+                                int act, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, float* state,
+                                cudaStream_t stream) {
+  return llmss_causal_conv_to(u, ldu, w, bias, out, LLMSS_F32, T_, C, taps, act, cu_q, seq_lens, slots, B, max_q, state, stream);
 }
 
 LLMSS_API int llmss_unary_f32(const float* x, int64_t ldx, void* out, int rows, int cols, int op, int out_dtype, cudaStream_t stream) {

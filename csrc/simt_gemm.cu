@@ -21,7 +21,8 @@ struct BgArgs {
   const void* x; int64_t ldx, sxh;
   const void* w; int64_t swh, swk, swn;
   const void* bias;              // [N] of T, h-independent, or null
-  const float* row_scale; int64_t lds;   // scale(t, h) = row_scale[t * lds + h], or null
+  const float* row_scale; int64_t lds;   // scale(t, h, n) = row_scale[t * lds + h * ssh + n * ssn], or null
+  int64_t ssh, ssn;                      // (1, 0): one factor per (token, head); (N, 1): one per output element
   void* out; int64_t ldo, soh;
   int M, N, K, H, act, act_start;
 };
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(NT) bgemm_kernel(BgArgs a) {
   for (int i = 0; i < 4; ++i) {
     const int m = m0 + ty * 4 + i;
     if (m >= a.M) continue;
-    const float rs = a.row_scale != nullptr ? a.row_scale[(int64_t)m * a.lds + h] : 1.f;
+    const float* rsp = a.row_scale != nullptr ? a.row_scale + (int64_t)m * a.lds + (int64_t)h * a.ssh : nullptr;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
@@ -90,6 +91,7 @@ __global__ void __launch_bounds__(NT) bgemm_kernel(BgArgs a) {
       float v = acc[i][j];
       if (bias != nullptr) v += to_f32(bias[n]);
       if (a.act != LLMSS_ACT_NONE && n >= a.act_start) v = act_sq(v, a.act);
+      const float rs = rsp != nullptr ? rsp[(int64_t)n * a.ssn] : 1.f;
       out[(int64_t)m * a.ldo + n] = from_f32<TO>(v * rs);
     }
   }
@@ -203,13 +205,13 @@ __global__ void __launch_bounds__(NT) bgemm_mma_kernel(BgArgs a) {
   for (int half = 0; half < 2; ++half) {
     const int m = m0 + wm * 16 + gid + half * 8;
     if (m >= a.M) continue;
-    const float rs = a.row_scale != nullptr ? a.row_scale[(int64_t)m * a.lds + h] : 1.f;
+    const float* rsp = a.row_scale != nullptr ? a.row_scale + (int64_t)m * a.lds + (int64_t)h * a.ssh : nullptr;
 #pragma unroll
     for (int f = 0; f < NF; ++f)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int n = n0 + wn * NW + f * 8 + tig * 2 + j;
-        if (n < a.N) out[(int64_t)m * a.ldo + n] = from_f32<TO>(acc[f][half * 2 + j] * rs);
+        if (n < a.N) out[(int64_t)m * a.ldo + n] = from_f32<TO>(acc[f][half * 2 + j] * (rsp != nullptr ? rsp[(int64_t)n * a.ssn] : 1.f));
       }
   }
 }
@@ -240,14 +242,16 @@ int launch_bg(const BgArgs& a, int out_f32, cudaStream_t stream) {
 
 }  // namespace
 
-LLMSS_API int llmss_bgemm_simt(const void* x, int64_t ldx, int64_t sxh, const void* w, int64_t swh, int64_t swk,
-                               int64_t swn, const void* bias, const float* row_scale, int64_t lds, void* out,
-                               int64_t ldo, int64_t soh, int M, int N, int K, int H, int act, int act_start,
-                               int dtype, int out_f32, cudaStream_t stream) {
+// scale(t, h, n) = row_scale[t * lds + h * ssh + n * ssn]: (ssh, ssn) = (1, 0) is one factor per token and head, (N, 1) one per
+// output element (an element-wise gate on the concatenated heads)
+LLMSS_API int llmss_bgemm_simt_ex(const void* x, int64_t ldx, int64_t sxh, const void* w, int64_t swh, int64_t swk,
+                                  int64_t swn, const void* bias, const float* row_scale, int64_t lds, int64_t ssh, int64_t ssn,
+                                  void* out, int64_t ldo, int64_t soh, int M, int N, int K, int H, int act, int act_start,
+                                  int dtype, int out_f32, cudaStream_t stream) {
   LLMSS_REQUIRE(M >= 0 && N > 0 && K > 0 && H > 0 && H <= 65535, "bgemm_simt: bad shape M=%d N=%d K=%d H=%d", M, N, K, H);
   LLMSS_REQUIRE((M + BM - 1) / BM <= 65535, "bgemm_simt: M=%d too large", M);
   if (M == 0) return 0;
-  BgArgs a{x, ldx, sxh, w, swh, swk, swn, bias, row_scale, lds, out, ldo, soh, M, N, K, H, act, act_start};
+  BgArgs a{x, ldx, sxh, w, swh, swk, swn, bias, row_scale, lds, ssh, ssn, out, ldo, soh, M, N, K, H, act, act_start};
   // 16-bit operands without bias / activation (the per-head products) take the tensor-core form; the 32-bit accumulators
   // are the same, so both forms agree to rounding of the summation order
   const bool mma_ok = dtype != LLMSS_F32 && bias == nullptr && act == LLMSS_ACT_NONE && (M + 127) / 128 <= 65535;
@@ -257,4 +261,12 @@ LLMSS_API int llmss_bgemm_simt(const void* x, int64_t ldx, int64_t sxh, const vo
   if (dtype == LLMSS_BF16) return launch_bg<__nv_bfloat16>(a, out_f32, stream);
   if (dtype == LLMSS_F16) return launch_bg<__half>(a, out_f32, stream);
   LLMSS_REQUIRE(false, "bgemm_simt: bad dtype %d", dtype);
+}
+
+LLMSS_API int llmss_bgemm_simt(const void* x, int64_t ldx, int64_t sxh, const void* w, int64_t swh, int64_t swk,
+                               int64_t swn, const void* bias, const float* row_scale, int64_t lds, void* out,
+                               int64_t ldo, int64_t soh, int M, int N, int K, int H, int act, int act_start,
+                               int dtype, int out_f32, cudaStream_t stream) {
+  return llmss_bgemm_simt_ex(x, ldx, sxh, w, swh, swk, swn, bias, row_scale, lds, 1, 0, out, ldo, soh, M, N, K, H, act, act_start,
+                             dtype, out_f32, stream);
 }

@@ -342,6 +342,54 @@ int llmss_delta_scan(const float* q, int64_t ldq, const float* k, int64_t ldk, c
                      const int* slots, int B, int max_q, int heads, int qk_heads, int dk, int dv, float unit_eps, float q_scale,
                      int beta_sigmoid, llmss_stream_t stream);
 
+/* ---- rotation by a frequency table, sandwich norms, gated linear recurrence inputs (csrc/rotary.cu) and the general forms they
+ * use elsewhere.  freq: n_pairs 64-bit frequencies (the first 2 n_pairs channels of a head rotate, the rest pass); mag multiplies
+ * cos and sin; interleaved: pairs (2i, 2i+1), else (i, i + n_pairs). */
+/* qk [T, hq*d + hkv*d] 32-bit: q, k rotated, unit_norm: every head / its rms; keys -> k_cache, the projected keys -> v_cache */
+int llmss_rope_norm_kv_write(const float* qk, int64_t ld, int hq, int hkv, int d, const double* freq, int n_pairs, float mag,
+                             int interleaved, int unit_norm, float eps, const int* positions, const int* slots, void* k_cache,
+                             void* v_cache, int block_size, void* q_out, int T, int dtype, llmss_stream_t stream);
+/* y [T, *] 32-bit: cq_out = rmsnorm(y[q_off .. + q_rank]) * qn_w; cache row = [rmsnorm(y[c_off .. + rank]) * cn_w | rotate(next
+ * rot columns) | zeros up to width]; gate = sigmoid(y[g_off .. + n_gate]) */
+int llmss_latent_rope_prep(const float* y, int64_t ldy, int q_off, int q_rank, int c_off, int rank, int rot, int g_off, int n_gate,
+                           const float* qn_w, const float* cn_w, float eps, const double* freq, int n_pairs, float mag,
+                           const int* positions, const int* slots, void* cache, int width, void* cq_out, float* gate, int T,
+                           int dtype, llmss_stream_t stream);
+/* q [T, H * (d + rot)] 32-bit -> q_nope [T, H * d] and the columns [rank, width) of every head of q_abs [T, H * width] */
+int llmss_latent_query_rope(const float* q, int64_t ldq, int H, int d, int rot, int rank, int width, const double* freq, int n_pairs,
+                            float mag, const int* positions, void* q_nope, void* q_abs, int abs_f32, int T, int dtype,
+                            llmss_stream_t stream);
+/* y [T, >= 2 n_qk] = [q | f | ..]: q = silu(q), k = 1 - f, lnf = ln f with f = lower + (1 - lower) sigmoid(f) */
+int llmss_hgrn_gates(const float* y, int64_t ldy, int n_qk, const float* lower, float* q, float* k, float* lnf, int T,
+                     llmss_stream_t stream);
+int llmss_softcap(float* z, int64_t ldz, int rows, int cols, float cap, llmss_stream_t stream);   /* z <- cap tanh(z / cap) */
+/* r = resid + rms_div(y) * w_post (y null: resid); hist given: hist[index] = r, and with depth_w r = sum_(j <= index) depth_w[j]
+ * hist[j]; out_r = r; w_next given: out_h = rms_div(r) * w_next in out_dtype */
+int llmss_sandwich_residual(const float* resid, int64_t ldr, const float* y, int64_t ldy, const float* w_post, float* hist,
+                            int index, const float* depth_w, const float* w_next, float* out_r, void* out_h, int T, int W, float eps,
+                            int out_dtype, llmss_stream_t stream);
+/* llmss_attention_window with a sink logit per head (sinks [hq] or null): exp(sinks[h]) joins every denominator of head h */
+int llmss_attention_sink(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                         int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias, int n_dist,
+                         const float* slopes, int window, const float* gate, int64_t ldg, const float* sinks, void* out, int B,
+                         int max_q, int hq, int hkv, int dk, int dv, float scale, int dtype, llmss_stream_t stream);
+/* llmss_moe_route with score_kind (0 softmax, 1 sigmoid), a per-expert correction added for the choice only (or null), groups
+ * scored by the sum of their group_top best, weights renormalised over the chosen experts or not */
+int llmss_moe_route_ex(const float* z, int64_t ldz, int T, int E, int top, int groups, int keep, float route_scale, int score_kind,
+                       const float* correction, int group_top, int renorm, int* ids, float* wts, float* dense, llmss_stream_t stream);
+/* llmss_causal_conv with the output in out_dtype */
+int llmss_causal_conv_to(const float* u, int64_t ldu, const float* w, const float* bias, void* out, int out_dtype, int T, int C,
+                         int taps, int act, const int* cu_q, const int* seq_lens, const int* slots, int B, int max_q, float* state,
+                         llmss_stream_t stream);
+/* llmss_embed_f32 with a factor on the token row */
+int llmss_embed_scaled_f32(const int* tokens, const int* positions, const void* wte, const void* wpe, float* out, int T, int H,
+                           int vocab, int max_pos, int pos_offset, int64_t ldo, float scale, int dtype, llmss_stream_t stream);
+/* llmss_bgemm_simt with scale(t, h, n) = row_scale[t * lds + h * ssh + n * ssn] */
+int llmss_bgemm_simt_ex(const void* x, int64_t ldx, int64_t sxh, const void* w, int64_t swh, int64_t swk, int64_t swn,
+                        const void* bias, const float* row_scale, int64_t lds, int64_t ssh, int64_t ssn, void* out, int64_t ldo,
+                        int64_t soh, int M, int N, int K, int H, int act, int act_start, int dtype, int out_f32,
+                        llmss_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -153,6 +153,29 @@ _SIGS = {
     "llmss_delta_scan": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                                  c_void_p]),
+    "llmss_moe_route_ex": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p]),
+    "llmss_attention_sink": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_float, c_int, c_void_p]),
+    "llmss_causal_conv_to": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "llmss_bgemm_simt_ex": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                    c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p]),
+    "llmss_embed_scaled_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64,
+                                       c_float, c_int, c_void_p]),
+    "llmss_rope_norm_kv_write": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_float, c_int, c_int, c_float,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "llmss_latent_rope_prep": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                       c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                       c_void_p]),
+    "llmss_latent_query_rope": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "llmss_hgrn_gates": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "llmss_softcap": (c_int, [c_void_p, c_int64, c_int, c_int, c_float, c_void_p]),
+    "llmss_sandwich_residual": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
 }
 _OPTIONAL = {
     "llmss_attn_decode_tc_bias": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,

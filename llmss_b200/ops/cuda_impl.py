@@ -413,14 +413,17 @@ def sample_vocab_parallel(local_logits, symm, vocab: int, greedy, temperature, t
 
 
 # --------------------------------------------------------------------------- 32-bit residual stream, Dynamic Tanh
-def embed_f32(tokens, wte, positions=None, wpe=None, pos_offset: int = 0):
+def embed_f32(tokens, wte, positions=None, wpe=None, pos_offset: int = 0, scale: float = 1.0, out=None):
     lib = _lib.load()
     T = tokens.numel()
     V, H = wte.shape
-    out = torch.empty(T, H, dtype=torch.float32, device=wte.device)
-    rc = lib.llmss_embed_f32(_ptr(tokens), _ptr(positions), _ptr(wte), _ptr(wpe), _ptr(out), T, H, V,
-                             wpe.shape[0] if wpe is not None else 0, pos_offset, out.stride(0), _DT[wte.dtype], _stream())
-    _lib.check(rc, "llmss_embed_f32")
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.float32, device=wte.device)
+    assert out.dtype == torch.float32 and out.shape == (T, H) and out.stride(1) == 1 and wte.is_contiguous()
+    rc = lib.llmss_embed_scaled_f32(_ptr(tokens), _ptr(positions), _ptr(wte), _ptr(wpe), _ptr(out), T, H, V,
+                                    wpe.shape[0] if wpe is not None else 0, pos_offset, out.stride(0), float(scale), _DT[wte.dtype],
+                                    _stream())
+    _lib.check(rc, "llmss_embed_scaled_f32")
     _count()
     return out
 
@@ -468,16 +471,26 @@ def latent_prep(y, q_off, c_off, g_off, n_q, rank, heads, norm_w, eps, slot_mapp
     return q, gate
 
 
-def heads_matmul(x, w, heads, k, n, w_is_kn, row_scale=None, out_dtype=None):
+def heads_matmul(x, w, heads, k, n, w_is_kn, row_scale=None, out_dtype=None, x_head_stride=None, elem_scale=None, out=None,
+                 out_head_stride=None):
     lib = _lib.load()
     T, _, ldx = _rows2d(x)
-    assert x.dtype == w.dtype and w.is_contiguous()
-    f32 = x.dtype == torch.float32 or out_dtype == torch.float32
-    out = torch.empty(T, heads * n, dtype=torch.float32 if f32 else x.dtype, device=x.device)
+    assert x.dtype == w.dtype and w.is_contiguous() and not (row_scale is not None and elem_scale is not None)
+    if out is None:
+        f32 = x.dtype == torch.float32 or out_dtype == torch.float32
+        out = torch.empty(T, heads * n, dtype=torch.float32 if f32 else x.dtype, device=x.device)
+    else:
+        f32 = out.dtype == torch.float32
+        assert f32 or out.dtype == x.dtype
+    assert out.stride(1) == 1
     swh, swk, swn = (k * n, n, 1) if w_is_kn else (n * k, 1, k)
-    rc = lib.llmss_bgemm_simt(_ptr(x), ldx, k, _ptr(w), swh, swk, swn, None, _ptr(row_scale),
-                              row_scale.stride(0) if row_scale is not None else 0, _ptr(out), out.stride(0), n, T, n, k, heads,
-                              ACT_NONE, 0, _DT[x.dtype], 1 if f32 else 0, _stream())
+    scale, lds, ssh, ssn = row_scale, (row_scale.stride(0) if row_scale is not None else 0), 1, 0
+    if elem_scale is not None:      # one factor per output element: [T, heads * n]
+        assert elem_scale.dtype == torch.float32 and elem_scale.stride(1) == 1
+        scale, lds, ssh, ssn = elem_scale, elem_scale.stride(0), n, 1
+    rc = lib.llmss_bgemm_simt_ex(_ptr(x), ldx, x_head_stride or k, _ptr(w), swh, swk, swn, None, _ptr(scale), lds, ssh, ssn, _ptr(out),
+                                 out.stride(0), out_head_stride or n, T, n, k, heads, ACT_NONE, 0, _DT[x.dtype], 1 if f32 else 0,
+                                 _stream())
     _lib.check(rc, "llmss_bgemm_simt(heads)")
     _count()
     return out
@@ -531,15 +544,17 @@ def latent_uses_tc(dtype, rank: int, block_size: int, heads: int) -> bool:
 
 
 # --------------------------------------------------------------------------- routed experts
-def moe_route(z, experts, top, groups, keep, route_scale, dense: bool = False):
+def moe_route(z, experts, top, groups, keep, route_scale, dense: bool = False, score: str = "softmax", correction=None,
+              group_top: int = 1, renorm: bool = True):
     lib = _lib.load()
     T, _, ldz = _rows2d(z)
     assert z.dtype == torch.float32
     ids = torch.empty(T, top, dtype=torch.int32, device=z.device)
     wts = torch.empty(T, top, dtype=torch.float32, device=z.device)
     dn = torch.empty(T, experts, dtype=torch.float32, device=z.device) if dense else None
-    rc = lib.llmss_moe_route(_ptr(z), ldz, T, experts, top, groups, keep, float(route_scale), _ptr(ids), _ptr(wts), _ptr(dn),
-                             _stream())
+    assert score in ("softmax", "sigmoid") and (correction is None or (correction.dtype == torch.float32 and correction.numel() == experts))
+    rc = lib.llmss_moe_route_ex(_ptr(z), ldz, T, experts, top, groups, keep, float(route_scale), 0 if score == "softmax" else 1,
+                                _ptr(correction), int(group_top), 1 if renorm else 0, _ptr(ids), _ptr(wts), _ptr(dn), _stream())
     _lib.check(rc, "llmss_moe_route")
     _count()
     return (ids, wts, dn) if dense else (ids, wts)
@@ -661,14 +676,15 @@ def token_shift(x, mu, batch, prev_state, out_dtype=None):
     return out
 
 
-def causal_conv(u, w, bias, act, batch, state):
+def causal_conv(u, w, bias, act, batch, state, out_dtype=None):
     lib = _lib.load()
     T, C, ldu = _f32rows(u)
     assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == C
-    out = torch.empty(T, C, dtype=torch.float32, device=u.device)
+    dt = out_dtype or torch.float32
+    out = torch.empty(T, C, dtype=dt, device=u.device)
     cu, sl, ss, B, mq = _bq(batch)
-    rc = lib.llmss_causal_conv(_ptr(u), ldu, _ptr(w), _ptr(bias), _ptr(out), T, C, w.shape[1], act, cu, sl, ss, B, mq, _ptr(state),
-                               _stream())
+    rc = lib.llmss_causal_conv_to(_ptr(u), ldu, _ptr(w), _ptr(bias), _ptr(out), _DT[dt], T, C, w.shape[1], act, cu, sl, ss, B, mq,
+                                  _ptr(state), _stream())
     _lib.check(rc, "llmss_causal_conv")
     _count()
     return out
@@ -841,12 +857,23 @@ from .reference import window_bias_table  # noqa: E402  (the window and slopes a
 
 
 def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias, gate=None, out_dtype=None, bias_over_scale=None,
-                   window=0, slopes=None):
+                   window=0, slopes=None, sinks=None):
     lib = _lib.load()
     T = q.shape[0]
     dt = q.dtype
     assert k_cache.dtype == dt and (out_dtype or dt) == dt and q.stride(1) == 1
     out = torch.empty(T, hq * dv, dtype=dt, device=q.device)
+    if sinks is not None:
+        # a sink logit per head in the softmax denominator: the generic kernel (any sizes, 32-bit scores, softmax and accumulation)
+        assert sinks.dtype == torch.float32 and sinks.numel() == hq
+        rc = lib.llmss_attention_sink(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
+                                      batch.block_tables.shape[1], k_cache.shape[2], _ptr(batch.seq_lens), _ptr(batch.cu_q),
+                                      _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _ptr(slopes),
+                                      int(window or 0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(sinks), _ptr(out),
+                                      batch.num_seqs, max(1, batch.max_q), hq, hkv, dk, dv, float(scale), _DT[dt], _stream())
+        _lib.check(rc, "llmss_attention_sink")
+        _count()
+        return out
     tc_ok = attention_bias_uses_tc(dt, dk, dv, k_cache.shape[2], scale) and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0
     table = None
     if window or slopes is not None:
@@ -896,3 +923,99 @@ def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias
     _lib.check(rc, "llmss_attention_bias")
     _count()
     return out
+
+
+# --------------------------------------------------------------------------- rotation by a table, sandwich norms
+_FREQ_DEV = {}
+
+
+def _freq_dev(freq, device):
+    """The 64-bit frequency table on the device, kept per (table, device) for the life of the process (a captured graph points at it)."""
+    key = (tuple(freq.tolist()), str(device))
+    t = _FREQ_DEV.get(key)
+    if t is None:
+        t = _FREQ_DEV[key] = freq.to(torch.float64).to(device).contiguous()
+    return t
+
+
+def rope_norm_kv_write(qk, hq, hkv, d, freq, mag, interleaved, unit_norm, eps, positions, slot_mapping, k_cache, v_cache, out_dtype=None):
+    lib = _lib.load()
+    T, _, ld = _f32rows(qk)
+    dt = out_dtype or k_cache.dtype
+    assert k_cache.dtype == dt and v_cache.dtype == dt and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[1:] == (hkv, k_cache.shape[2], d) and v_cache.shape == k_cache.shape
+    q = torch.empty(T, hq * d, dtype=dt, device=qk.device)
+    rc = lib.llmss_rope_norm_kv_write(_ptr(qk), ld, hq, hkv, d, _ptr(_freq_dev(freq, qk.device)), freq.numel(), float(mag),
+                                      1 if interleaved else 0, 1 if unit_norm else 0, float(eps), _ptr(positions), _ptr(slot_mapping),
+                                      _ptr(k_cache), _ptr(v_cache), k_cache.shape[2], _ptr(q), T, _DT[dt], _stream())
+    _lib.check(rc, "llmss_rope_norm_kv_write")
+    _count()
+    return q
+
+
+def latent_rope_prep(y, q_off, q_rank, c_off, rank, rot, g_off, n_gate, qn_w, cn_w, eps, freq, mag, positions, slot_mapping, cache, dtype):
+    lib = _lib.load()
+    T, _, ldy = _f32rows(y)
+    assert cache.dtype == dtype and cache.is_contiguous() and cn_w.dtype == torch.float32 and (q_rank == 0 or qn_w.dtype == torch.float32)
+    cq = torch.empty(T, q_rank, dtype=dtype, device=y.device) if q_rank > 0 else None
+    gate = torch.empty(T, n_gate, dtype=torch.float32, device=y.device) if n_gate > 0 else None
+    rc = lib.llmss_latent_rope_prep(_ptr(y), ldy, q_off, q_rank, c_off, rank, rot, g_off, n_gate, _ptr(qn_w), _ptr(cn_w), float(eps),
+                                    _ptr(_freq_dev(freq, y.device)), freq.numel(), float(mag), _ptr(positions), _ptr(slot_mapping),
+                                    _ptr(cache), cache.shape[-1], _ptr(cq), _ptr(gate), T, _DT[dtype], _stream())
+    _lib.check(rc, "llmss_latent_rope_prep")
+    _count()
+    return cq, gate
+
+
+def latent_query_rope(q, heads, d, rot, rank, width, freq, mag, positions, dtype, abs_dtype):
+    lib = _lib.load()
+    T, _, ldq = _f32rows(q)
+    assert abs_dtype in (torch.float32, dtype)
+    q_nope = torch.empty(T, heads * d, dtype=dtype, device=q.device)
+    q_abs = torch.empty(T, heads * width, dtype=abs_dtype, device=q.device)
+    rc = lib.llmss_latent_query_rope(_ptr(q), ldq, heads, d, rot, rank, width, _ptr(_freq_dev(freq, q.device)), freq.numel(), float(mag),
+                                     _ptr(positions), _ptr(q_nope), _ptr(q_abs), 1 if abs_dtype == torch.float32 else 0, T, _DT[dtype],
+                                     _stream())
+    _lib.check(rc, "llmss_latent_query_rope")
+    _count()
+    return q_nope, q_abs
+
+
+def hgrn_gates(y, n_qk, lower):
+    lib = _lib.load()
+    T, C, ldy = _f32rows(y)
+    assert C >= 2 * n_qk and lower.dtype == torch.float32 and lower.numel() == n_qk
+    q, k, lnf = (torch.empty(T, n_qk, dtype=torch.float32, device=y.device) for _ in range(3))
+    _lib.check(lib.llmss_hgrn_gates(_ptr(y), ldy, n_qk, _ptr(lower), _ptr(q), _ptr(k), _ptr(lnf), T, _stream()), "llmss_hgrn_gates")
+    _count()
+    return q, k, lnf
+
+
+def sandwich_residual(resid, y, w_post, eps, w_next=None, history=None, index=0, depth_w=None, out_dtype=None):
+    lib = _lib.load()
+    T, W, ldr = _f32rows(resid)
+    ldy = 0
+    if y is not None:
+        _, Wy, ldy = _f32rows(y)
+        assert Wy == W and w_post.dtype == torch.float32 and w_post.numel() == W
+    if history is not None:
+        assert history.dtype == torch.float32 and history.is_contiguous() and history.shape[1:] == (T, W) and index < history.shape[0]
+        assert depth_w is None or (depth_w.dtype == torch.float32 and depth_w.numel() >= index + 1)
+    dt = out_dtype or torch.float32
+    out_r = torch.empty(T, W, dtype=torch.float32, device=resid.device)
+    out_h = torch.empty(T, W, dtype=dt, device=resid.device) if w_next is not None else None
+    assert w_next is None or (w_next.dtype == torch.float32 and w_next.numel() == W)
+    rc = lib.llmss_sandwich_residual(_ptr(resid), ldr, _ptr(y), ldy, _ptr(w_post), _ptr(history), int(index),
+                                     _ptr(depth_w) if history is not None else None, _ptr(w_next), _ptr(out_r), _ptr(out_h), T, W,
+                                     float(eps), _DT[dt], _stream())
+    _lib.check(rc, "llmss_sandwich_residual")
+    _count()
+    return out_h, out_r
+
+
+def softcap(z, cap):
+    lib = _lib.load()
+    assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1
+    _lib.check(lib.llmss_softcap(_ptr(z), z.stride(0), z.shape[0], z.shape[1], float(cap), _stream()), "llmss_softcap")
+    _count()
+    return z

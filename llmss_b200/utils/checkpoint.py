@@ -359,6 +359,112 @@ PRESETS.update({
 })
 
 
+def zenorax_config(width: int, vocab: int, layers, taps: int = 3, embed_scale: float = 1.0, softcap: float = 30.0,
+                   eps: float = 1e-6) -> dict:
+    """config.json of a Zenorax model.  ``layers``: one dict per layer,
+    {"type": "latent_attention", heads, dim, rot_dim, vdim, kv_rank, q_rank, optionally scale, base, scaling} |
+    {"type": "attention", heads, kv_heads, dim, optionally rot_dims, scale, base, scaling} | {"type": "hgrn2", heads, dim, vdim},
+    each with "mlp": None | {"experts", "top", "ff", optionally "groups", "keep"}.  ``scaling``: None | {"factor"} (linear) |
+    {"factor", "original", "fast", "slow"} (YaRN)."""
+    out = []
+    for L in layers:
+        t = L["type"]
+        if t == "latent_attention":
+            rot = {"base": L.get("base", 10000.0), "dims": L.get("rot_dims", L["rot_dim"])}
+            if L.get("scaling"):
+                rot["scaling"] = dict(L["scaling"])
+            m = {k: L[k] for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank")}
+            m.update(rot=rot, scale=L.get("scale", (L["dim"] + L["rot_dim"]) ** -0.5))
+        elif t == "attention":
+            rot = {"base": L.get("base", 10000.0), "dims": L.get("rot_dims", L["dim"])}
+            if L.get("scaling"):
+                rot["scaling"] = dict(L["scaling"])
+            m = {"heads": L["heads"], "kv_heads": L["kv_heads"], "dim": L["dim"], "vdim": L["dim"], "rot": rot,
+                 "scale": L.get("scale", L["dim"] ** -0.5)}
+        else:
+            m = {k: L[k] for k in ("heads", "dim", "vdim")}
+        f = L.get("mlp")
+        mlp = None
+        if f is not None:
+            mlp = {"kind": "moe", "expert": {"ff": f["ff"]},
+                   "router": {"experts": f["experts"], "top": f["top"], "groups": {"count": f.get("groups", 1), "keep": f.get("keep", 1)}}}
+        out.append({"type": t, "mixer": m, "mlp": mlp})
+    return {"architecture": "Zenorax", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed_scale},
+            "canon": {"taps": taps}, "logit_softcap": softcap, "layers": out}
+
+
+def _zenorax_shapes(cfg: dict):
+    W, V, taps = cfg["width"], cfg["vocab"], cfg["canon"]["taps"]
+    yield "embed", (V, W), ("n", 0.0, 1.0 / cfg["embedding"]["scale"])
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}", L["mixer"]
+        q = f"{p}.mix"
+        for nm in ("norm1", "norm1b") + (("norm2", "norm2b") if L.get("mlp") is not None else ()):
+            yield f"{p}.{nm}", (W,), "ln_w"
+        yield f"{p}.canon1", (W, taps), ("n", 0.0, 0.3)
+        yield f"{p}.dwa", (i + 2,), ("dwa", 0.0, 0.0)
+        if L["type"] == "latent_attention":
+            H, d, r, dv, R, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            yield f"{q}.dq", (Q, W), "fan"
+            yield f"{q}.dq.norm", (Q,), "ln_w"
+            yield f"{q}.uq", (H * (d + r), Q), "fan"
+            yield f"{q}.dkv", (R + r, W), "fan"
+            yield f"{q}.dkv.norm", (R,), "ln_w"
+            yield f"{q}.uk", (H * d, R), "fan"
+            yield f"{q}.uv", (H * dv, R), "fan"
+            yield f"{q}.g", (H * dv, W), "fan"
+            yield f"{q}.o", (W, H * dv), "fan"
+        elif L["type"] == "attention":
+            H, G, d = m["heads"], m["kv_heads"], m["dim"]
+            yield f"{q}.q", (H * d, W), "fan"
+            yield f"{q}.k", (G * d, W), "fan"
+            yield f"{q}.sink", (H,), ("n", 0.0, 1.0)
+            yield f"{q}.o", (W, H * d), "fan"
+        else:
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            yield f"{q}.q", (H * d, W), "fan"
+            yield f"{q}.f", (H * d, W), "fan"
+            yield f"{q}.f.b", (H * d,), ("n", 1.0, 1.0)
+            yield f"{q}.lower", (H * d,), ("u", 0.0, 0.9)
+            yield f"{q}.v", (H * dv, W), "fan"
+            yield f"{q}.norm", (dv,), "ln_w"
+            yield f"{q}.o", (W, H * dv), "fan"
+        f = L.get("mlp")
+        if f is not None:
+            E, F = f["router"]["experts"], f["expert"]["ff"]
+            yield f"{p}.mlp.router", (E, W), "fan2"
+            yield f"{p}.mlp.correction", (E,), ("n", 0.0, 0.1)
+            for e in range(E):
+                yield f"{p}.mlp.e{e}.up", (F, W), "fan"
+                yield f"{p}.mlp.e{e}.down", (W, F), "fan"
+    yield "final.norm", (W,), "ln_w"
+
+
+def _zenorax_preset(width, vocab, heads, n_blocks, experts=16, top=4, groups=4, keep=2, eff=1024):
+    """``n_blocks`` x (latent attention, sink attention, HGRN2), every layer with routed experts; head size 128.  The latent
+    row is 192 + 64 = 256 numbers, a size the tensor-core multi-query kernels take."""
+    mlp = dict(experts=experts, top=top, groups=groups, keep=keep, ff=eff)
+    lat = dict(type="latent_attention", heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=192, q_rank=width // 2,
+               scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}, mlp=mlp)
+    att = dict(type="attention", heads=heads, kv_heads=max(1, heads // 4), dim=128, scaling={"factor": 2.0}, mlp=mlp)
+    rec = dict(type="hgrn2", heads=heads, dim=128, vdim=128, mlp=mlp)
+    return zenorax_config(width, vocab, [dict(L) for _ in range(n_blocks) for L in (lat, att, rec)], taps=4, embed_scale=width ** 0.5)
+
+
+PRESETS.update({
+    "zenorax-tiny": zenorax_config(128, 320, [
+        dict(type="latent_attention", heads=4, dim=16, rot_dim=8, vdim=24, kv_rank=40, q_rank=48,
+             scaling={"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}, mlp=dict(experts=8, top=2, groups=4, keep=2, ff=32)),
+        dict(type="attention", heads=4, kv_heads=2, dim=24, rot_dims=16, scaling={"factor": 2.0}, mlp=None),
+        dict(type="hgrn2", heads=2, dim=24, vdim=40, mlp=dict(experts=4, top=1, groups=1, keep=1, ff=48)),
+        dict(type="latent_attention", heads=2, dim=24, rot_dim=16, vdim=16, kv_rank=48, q_rank=32, mlp=dict(experts=6, top=3, groups=2, keep=1, ff=32))],
+        taps=3, embed_scale=8.0),
+    # sizes whose layers resemble a served model's (random weights), beside gptj-like-* of equal width and depth
+    "zenorax-2k": _zenorax_preset(2048, 32000, 16, 6),
+    "zenorax-4k": _zenorax_preset(4096, 32000, 32, 6, experts=32, eff=1536, groups=8, keep=4),
+})
+
+
 def _shapes(cfg: dict) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
     """(name, shape, kind) for every tensor of the family; kind in {w, b, ln_w, ln_b, emb} (and, for architectures whose
     activations must keep unit scale without trained weights: unit, fan, fan2, alpha, ls)."""
@@ -369,6 +475,8 @@ def _shapes(cfg: dict) -> Iterator[Tuple[str, Tuple[int, ...], str]]:
         yield from _ninelix_shapes(cfg)
     elif mt == "botalorn":
         yield from _botalorn_shapes(cfg)
+    elif mt == "zenorax":
+        yield from _zenorax_shapes(cfg)
     elif mt == "gptj":
         H, L, V = cfg["n_embd"], cfg["n_layer"], cfg["vocab_size"]
         F = cfg.get("n_inner") or 4 * H
@@ -510,10 +618,14 @@ def write_random_checkpoint(path, preset_or_cfg, dtype=torch.float16, device=Non
             shard, size = {}, 0
 
     for name, shape, kind in _shapes(cfg):
-        if isinstance(kind, tuple):      # ("n", mean, std): normal; ("u", lo, hi): uniform; ("hcmix", diagonal, std): near a scaled identity
+        if isinstance(kind, tuple):      # ("n", mean, std): normal; ("u", lo, hi): uniform; ("hcmix", diagonal, std): near a scaled identity;
+            # ("dwa", ..): depth-averaging weights
             r = (torch.rand if kind[0] == "u" else torch.randn)(shape, generator=gen, device=device, dtype=torch.float32)
             if kind[0] == "hcmix":
                 t = kind[1] * torch.eye(shape[0], device=device) + kind[2] * r
+            elif kind[0] == "dwa":      # depth-averaging weights: mostly the newest layer output, a little of every older one
+                t = 0.1 * r.abs() / shape[0]
+                t[-1] = 1.0
             else:
                 t = kind[1] + kind[2] * r if kind[0] == "n" else kind[1] + (kind[2] - kind[1]) * r
         elif kind in ("unit", "fan", "fan2", "alpha", "ls"):
