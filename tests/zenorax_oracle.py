@@ -12,10 +12,6 @@ def rms_div(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 # ----------------------------------------------------------------------------------------------- rotary positions
 def rotary_frequencies(rot):
     """(frequency per pair [dims / 2], factor on cos and sin) for a ``rot`` entry {base, dims, scaling}."""
@@ -191,3 +187,16 @@ def forward(cfg, p, tokens, taps=None):
     z = (rms_div(x, eps) * p["final.norm"]) @ p["embed"].T
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(z / cap) if cap else z
+
+
+def load_weights(path):
+    """Every tensor of a checkpoint folder as float64."""
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    out = {}
+    for f in sorted(Path(path).glob("*.safetensors")):
+        for k, v in load_file(str(f)).items():
+            out[k] = v.double()
+    return out
