@@ -54,7 +54,8 @@ def parse():
     ap.add_argument("--profile-ops", action="store_true", help="eager decode with per-op CUDA-event timing (diagnostic)")
     ap.add_argument("--compare", default=None, metavar="A:B[,A:B...]",
                     help="instead of the headline run: prefill and decode tokens/s plus per-op device times of preset A beside "
-                         "preset B (e.g. bedovik-2k:gptj-like-2k, ninelix-2k:gptj-like-2k, botalorn-2k:gptj-like-2k), one JSON line per preset")
+                         "preset B (e.g. bedovik-2k:gptj-like-2k, ninelix-2k:gptj-like-2k, botalorn-2k:gptj-like-2k, zenorax-2k:gptj-like-2k), "
+                         "one JSON line per preset")
     return ap.parse_args()
 
 

@@ -234,13 +234,16 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(
 
 template <typename T, int D>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           T* __restrict__ out, int64_t ldo, int hq, int num_splits) {
+                                           T* __restrict__ out, int64_t ldo, int hq, int num_splits,
+                                           const float* __restrict__ sinks) {
   pdl_launch_dependents();
   pdl_wait();
   const int head = blockIdx.x, b = blockIdx.y;
   const int64_t base = ((int64_t)b * hq + head) * num_splits;
   float mn = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mn = fmaxf(mn, part_ml[(base + s) * 2]);
+  // an attention sink: one more term in the denominator (the maxima are in log2 units)
+  const float sink_l = (sinks != nullptr && mn > -INFINITY) ? exp2f(sinks[head] * 1.4426950408889634f - mn) : 0.f;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float lt = 0.f, at = 0.f;
     for (int s = 0; s < num_splits; ++s) {
@@ -249,7 +252,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
       lt += part_ml[(base + s) * 2 + 1] * sc;
       at += part_o[(base + s) * D + c] * sc;
     }
-    out[(int64_t)b * ldo + (int64_t)head * D + c] = from_f32<T>(lt > 0.f ? at / lt : 0.f);
+    out[(int64_t)b * ldo + (int64_t)head * D + c] = from_f32<T>(lt > 0.f ? at / (lt + sink_l) : 0.f);
   }
 }
 
@@ -270,7 +273,7 @@ int launch_decode(const void* q, int64_t ldq, const void* kc, const void* vc, co
   LLMSS_CHECK_CUDA(cudaGetLastError());
   if (num_splits > 1) {
     attn_decode_combine_kernel<T, D><<<dim3(hq, B), (D < 128 ? D : 128), 0, stream>>>(part_o, part_ml, (T*)out, ldo, hq,
-                                                                                    num_splits);
+                                                                                    num_splits, nullptr);
     LLMSS_CHECK_CUDA(cudaGetLastError());
   }
   return 0;
@@ -336,14 +339,23 @@ LLMSS_API int llmss_attn_decode_pick_splits(int B, int hq, int hkv, int d, int m
 
 // Merge the split-KV partials ([B, hq, splits, d] + [B, hq, splits, 2]) into `out`; shared with the
 // tensor-core decode kernel (attn_decode_tc.cu).
+LLMSS_API int llmss_attn_decode_combine_sink(const float* part_o, const float* part_ml, void* out, int64_t ldo, int B, int hq,
+                                             int d, int num_splits, int dtype, const float* sinks, cudaStream_t stream);
+
 LLMSS_API int llmss_attn_decode_combine(const float* part_o, const float* part_ml, void* out, int64_t ldo, int B, int hq,
                                         int d, int num_splits, int dtype, cudaStream_t stream) {
+  return llmss_attn_decode_combine_sink(part_o, part_ml, out, ldo, B, hq, d, num_splits, dtype, nullptr, stream);
+}
+
+// sinks [hq] or null: exp(sinks[h]) joins the denominator of head h
+LLMSS_API int llmss_attn_decode_combine_sink(const float* part_o, const float* part_ml, void* out, int64_t ldo, int B, int hq,
+                                             int d, int num_splits, int dtype, const float* sinks, cudaStream_t stream) {
   LLMSS_REQUIRE(d == 64 || d == 128 || d == 256, "attn_decode_combine: head_dim=%d unsupported", d);
   if (B == 0) return 0;
   const dim3 grid(hq, B);
   const int threads = d < 128 ? d : 128;
 #define LLMSS_C(T_, D_) \
-  LLMSS_CHECK_CUDA(launch_pdl(attn_decode_combine_kernel<T_, D_>, grid, dim3(threads), 0, stream, part_o, part_ml, (T_*)out, ldo, hq, num_splits))
+  LLMSS_CHECK_CUDA(launch_pdl(attn_decode_combine_kernel<T_, D_>, grid, dim3(threads), 0, stream, part_o, part_ml, (T_*)out, ldo, hq, num_splits, sinks))
   if (dtype == LLMSS_F16) {
     if (d == 64) LLMSS_C(__half, 64); else if (d == 128) LLMSS_C(__half, 128); else LLMSS_C(__half, 256);
   } else if (dtype == LLMSS_BF16) {

@@ -61,6 +61,8 @@ struct DArgs {
   const float* bias;   // optional additive score bias [hq][n_dist] in raw-score units (bias / scale), indexed by the
   int n_dist;          // distance of the key from the query (= the sequence's last token); last column = all larger ones
   int dtype;
+  const float* sinks;  // optional attention sink per q head: 2^(sinks[h] log2 e) joins the denominator (here when an item
+                       // covers its whole sequence, else in the combine pass)
 };
 
 struct Item {
@@ -615,7 +617,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (!owner && !a.ws) continue;
       mbar_wait(&bar_o[(g - 1) & 1], ((g - 1) >> 1) & 1, 72);
       tcgen05_fence_after();
-      const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+      float l_all = l_run;
+      if (a.sinks != nullptr && I.direct && live && l_run > 0.f) l_all += exp2f(a.sinks[head] * 1.4426950408889634f - m_run);
+      const float inv_l = l_all > 0.f ? 1.0f / l_all : 0.f;
       const int e_cols = a.ws ? D / 4 : D;            // head-dim columns this warp holds ...
       const int e_base = a.ws ? quarter * (D / 4) : 0;  // ... starting at this head-dim column
 #pragma unroll 1
@@ -662,7 +666,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 template <typename T, int D>
 __global__ void attn_decode_tc_balanced_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                        T* __restrict__ out, int64_t ldo, const int* __restrict__ seq_lens,
-                                                       int B, int hq, int hkv, int max_parts, int grid_main, int bn) {
+                                                       int B, int hq, int hkv, int max_parts, int grid_main, int bn,
+                                                       const float* __restrict__ sinks) {
   pdl_launch_dependents();
   pdl_wait();
   const int head = blockIdx.x, b = blockIdx.y;
@@ -688,6 +693,7 @@ __global__ void attn_decode_tc_balanced_combine_kernel(const float* __restrict__
   const int64_t base = ((int64_t)b * hq + head) * max_parts;
   float mn = -INFINITY;
   for (int s = 0; s < parts; ++s) mn = fmaxf(mn, part_ml[(base + s) * 2]);
+  const float sink_l = (sinks != nullptr && mn > -INFINITY) ? exp2f(sinks[head] * 1.4426950408889634f - mn) : 0.f;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float lt = 0.f, at = 0.f;
     for (int s = 0; s < parts; ++s) {
@@ -696,7 +702,7 @@ __global__ void attn_decode_tc_balanced_combine_kernel(const float* __restrict__
       lt += part_ml[(base + s) * 2 + 1] * sc;
       at += part_o[(base + s) * D + c] * sc;
     }
-    orow[c] = from_f32<T>(lt > 0.f ? at / lt : 0.f);
+    orow[c] = from_f32<T>(lt > 0.f ? at / (lt + sink_l) : 0.f);
   }
 }
 
@@ -762,6 +768,8 @@ LLMSS_API int64_t llmss_attn_decode_tc_balanced_scratch_floats(int B, int hq, in
   return (int64_t)B * hq * balanced_max_parts(max_blocks, block_size, tile_keys(d)) * (d + 2);
 }
 
+extern "C" int llmss_attn_decode_combine_sink(const float* part_o, const float* part_ml, void* out, int64_t ldo, int B, int hq,
+                                              int d, int num_splits, int dtype, const float* sinks, cudaStream_t stream);
 extern "C" int llmss_attn_decode_combine(const float* part_o, const float* part_ml, void* out, int64_t ldo, int B, int hq,
                                          int d, int num_splits, int dtype, cudaStream_t stream);
 
@@ -804,7 +812,7 @@ LLMSS_API int llmss_attn_decode_tc_supported(int hq, int hkv, int d, int block_s
 static int decode_tc_impl(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                           int max_blocks, const int* seq_lens, void* out, int64_t ldo, float* scratch, int B, int hq, int hkv, int d,
                           int block_size, int num_blocks, float scale, int num_splits, int dtype, const float* bias, int n_dist,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const float* sinks = nullptr) {
   LLMSS_REQUIRE(dtype == LLMSS_F16 || dtype == LLMSS_BF16, "attn_decode_tc: dtype must be f16/bf16");
   LLMSS_REQUIRE(d == 64 || d == 128 || d == 256, "attn_decode_tc: head_dim=%d unsupported", d);
   LLMSS_REQUIRE(hq > 0 && hkv > 0, "attn_decode_tc: head counts must be positive (hq=%d hkv=%d)", hq, hkv);
@@ -884,6 +892,7 @@ static int decode_tc_impl(const void* q, int64_t ldq, const void* k_cache, const
   a.dtype = dtype;
   a.bias = bias;
   a.n_dist = n_dist;
+  a.sinks = sinks;
   int rc = 0;
 #define LLMSS_DT(T_, D_)                                                         \
   do {                                                                           \
@@ -908,7 +917,7 @@ static int decode_tc_impl(const void* q, int64_t ldq, const void* k_cache, const
 #define LLMSS_BC(T_, D_)                                                                                             \
   LLMSS_CHECK_CUDA(launch_pdl(attn_decode_tc_balanced_combine_kernel<T_, D_>, cgrid, dim3(threads), 0, stream, \
                               (const float*)a.part_o, (const float*)a.part_ml, (T_*)out, ldo, seq_lens, B, hq, hkv,  \
-                              max_parts, sm_count(), a.bn))
+                              max_parts, sm_count(), a.bn, a.sinks))
     if (dtype == LLMSS_F16) {
       if (d == 64) LLMSS_BC(__half, 64); else if (d == 128) LLMSS_BC(__half, 128); else LLMSS_BC(__half, 256);
     } else {
@@ -917,7 +926,7 @@ static int decode_tc_impl(const void* q, int64_t ldq, const void* k_cache, const
 #undef LLMSS_BC
     return 0;
   }
-  return llmss_attn_decode_combine(a.part_o, a.part_ml, out, ldo, B, hq, d, num_splits, dtype, stream);
+  return llmss_attn_decode_combine_sink(a.part_o, a.part_ml, out, ldo, B, hq, d, num_splits, dtype, a.sinks, stream);
 }
 
 LLMSS_API int llmss_attn_decode_tc(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
@@ -936,4 +945,16 @@ LLMSS_API int llmss_attn_decode_tc_bias(const void* q, int64_t ldq, const void* 
   LLMSS_REQUIRE(bias_over_scale != nullptr && n_dist > 0 && scale > 0.f, "attn_decode_tc_bias: needs a bias table and a positive scale");
   return decode_tc_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, scratch, B, hq, hkv, d, block_size,
                         num_blocks, scale, num_splits, dtype, bias_over_scale, n_dist, stream);
+}
+
+// The same with an attention sink per q head (sinks [hq] 32-bit): exp(sinks[h]) joins the softmax denominator of head h.
+// bias_over_scale may be null.
+LLMSS_API int llmss_attn_decode_tc_sink(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                                        const int* block_tables, int max_blocks, const int* seq_lens, void* out, int64_t ldo,
+                                        float* scratch, int B, int hq, int hkv, int d, int block_size, int num_blocks, float scale,
+                                        int num_splits, int dtype, const float* bias_over_scale, int n_dist, const float* sinks,
+                                        cudaStream_t stream) {
+  LLMSS_REQUIRE(scale > 0.f && (bias_over_scale == nullptr || n_dist > 0), "attn_decode_tc_sink: needs a positive scale");
+  return decode_tc_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, scratch, B, hq, hkv, d, block_size,
+                        num_blocks, scale, num_splits, dtype, bias_over_scale, n_dist, stream, sinks);
 }

@@ -85,6 +85,8 @@ struct PArgs {
   int n_dist;
   const float* gate;
   int64_t ldg;
+  // and an attention sink per head: 2^(sinks[h] * log2 e) joins every denominator of head h (no key, no value, not scaled)
+  const float* sinks;
 };
 
 // MN-major (N contiguous) 128B-swizzled operand: rows are K (keys), 64 elements of N per 128-byte row;
@@ -405,7 +407,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_sfree[j & 1]);  // S_j is in registers: the buffer can take QK_{j+2}
-      if constexpr (BIAS) {
+      if (BIAS && a.bias != nullptr) {
         const float* bt = a.bias + (int64_t)head * a.n_dist;
         const int dmax = a.n_dist - 1, d0 = qpos - kbase;   // distance from this row to the tile's first key
         if (d0 - (BN - 1) >= dmax) {                        // the whole tile lies at or beyond the table's last column
@@ -502,6 +504,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     // epilogue: O / l -> out
     mbar_wait(&bar_o[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 72);
     tcgen05_fence_after();
+    if constexpr (BIAS) {
+      if (a.sinks != nullptr && l_run > 0.f) l_run += exp2f(a.sinks[head] * 1.4426950408889634f - m_run);
+    }
     float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
     if constexpr (BIAS) {
       if (a.gate != nullptr && qrow < len) inv_l *= 1.0f / (1.0f + __expf(-a.gate[(int64_t)(seq_start + qrow) * a.ldg + head]));
@@ -644,7 +649,8 @@ LLMSS_API int llmss_attn_prefill(const void* q, int64_t ldq, const void* k, int6
 static int prefill_paged_impl(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
                               int max_blocks, const int* seq_lens, void* out, int64_t ldo, const int* cu_q, int num_seqs, int max_q,
                               int total_q, int hq, int hkv, int d, int block_size, int num_blocks, float scale, int dtype,
-                              const float* bias, int n_dist, const float* gate, int64_t ldg, cudaStream_t stream) {
+                              const float* bias, int n_dist, const float* gate, int64_t ldg, cudaStream_t stream,
+                              const float* sinks = nullptr) {
   LLMSS_REQUIRE(dtype == LLMSS_F16 || dtype == LLMSS_BF16, "attn_prefill_paged: dtype must be f16/bf16");
   LLMSS_REQUIRE(d == 64 || d == 128 || d == 256, "attn_prefill_paged: head_dim=%d unsupported (64/128/256)", d);
   LLMSS_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attn_prefill_paged: bad head grouping hq=%d hkv=%d", hq, hkv);
@@ -677,8 +683,10 @@ static int prefill_paged_impl(const void* q, int64_t ldq, const void* k_cache, c
   a.n_dist = n_dist;
   a.gate = gate;
   a.ldg = ldg;
+  a.sinks = sinks;
+  const bool extras = bias != nullptr || gate != nullptr || sinks != nullptr;
 #define LLMSS_PP(T_, D_)                                                                                  \
-  return bias != nullptr ? launch_prefill<T_, D_, true, true>(tm, tk, tv, a, num_seqs, max_q, stream)     \
+  return extras ? launch_prefill<T_, D_, true, true>(tm, tk, tv, a, num_seqs, max_q, stream)     \
                          : launch_prefill<T_, D_, true, false>(tm, tk, tv, a, num_seqs, max_q, stream)
   if (dtype == LLMSS_F16) {
     if (d == 64) LLMSS_PP(__half, 64);
@@ -711,4 +719,16 @@ LLMSS_API int llmss_attn_prefill_paged_bias(const void* q, int64_t ldq, const vo
   LLMSS_REQUIRE(bias_over_scale != nullptr && n_dist > 0 && scale > 0.f, "attn_prefill_paged_bias: needs a bias table and a positive scale");
   return prefill_paged_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, cu_q, num_seqs, max_q, total_q,
                             hq, hkv, d, block_size, num_blocks, scale, dtype, bias_over_scale, n_dist, gate, ldg, stream);
+}
+
+// The same with an attention sink per head (sinks [hq] 32-bit): exp(sinks[h]) joins every softmax denominator of head h.
+// bias_over_scale / gate may be null.
+LLMSS_API int llmss_attn_prefill_paged_sink(const void* q, int64_t ldq, const void* k_cache, const void* v_cache,
+                                            const int* block_tables, int max_blocks, const int* seq_lens, void* out, int64_t ldo,
+                                            const int* cu_q, int num_seqs, int max_q, int total_q, int hq, int hkv, int d,
+                                            int block_size, int num_blocks, float scale, int dtype, const float* bias_over_scale,
+                                            int n_dist, const float* gate, int64_t ldg, const float* sinks, cudaStream_t stream) {
+  LLMSS_REQUIRE(scale > 0.f && (bias_over_scale == nullptr || n_dist > 0), "attn_prefill_paged_sink: needs a positive scale");
+  return prefill_paged_impl(q, ldq, k_cache, v_cache, block_tables, max_blocks, seq_lens, out, ldo, cu_q, num_seqs, max_q, total_q,
+                            hq, hkv, d, block_size, num_blocks, scale, dtype, bias_over_scale, n_dist, gate, ldg, stream, sinks);
 }

@@ -178,6 +178,12 @@ _SIGS = {
                                         c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
 }
 _OPTIONAL = {
+    "llmss_attn_decode_tc_sink": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
+                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                          c_int, c_void_p, c_void_p]),
+    "llmss_attn_prefill_paged_sink": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
+                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                              c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "llmss_attn_decode_tc_bias": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64,
                                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
                                           c_int, c_void_p]),

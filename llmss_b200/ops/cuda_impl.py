@@ -224,8 +224,10 @@ def use_tc_decode(hq: int, hkv: int, d: int, block_size: int = 16) -> bool:
     return block_size == 64 or g >= _TC_MIN_GROUP
 
 
-def attn_decode(q_view, k_cache, v_cache, block_tables, seq_lens, out_view, hq, hkv, d, scale, num_splits, bias_over_scale=None):
-    """``bias_over_scale`` [hq, n_dist] (tensor-core kernel only): additive score bias per head and key distance."""
+def attn_decode(q_view, k_cache, v_cache, block_tables, seq_lens, out_view, hq, hkv, d, scale, num_splits, bias_over_scale=None,
+                sinks=None):
+    """``bias_over_scale`` [hq, n_dist] (tensor-core kernel only): additive score bias per head and key distance.
+    ``sinks`` [hq] 32-bit (tensor-core kernel only): a sink logit per head in the softmax denominator."""
     lib = _lib.load()
     B = q_view.shape[0]
     bs = k_cache.shape[2]
@@ -239,7 +241,16 @@ def attn_decode(q_view, k_cache, v_cache, block_tables, seq_lens, out_view, hq, 
     elif num_splits == 0:
         n = lib.llmss_attn_decode_tc_balanced_scratch_floats(B, hq, d, block_tables.shape[1], bs)
         scratch = arena(q_view.device).attn_scratch(n, q_view.device)
-    assert bias_over_scale is None or tc, "the score bias rides on the tensor-core decode kernel only"
+    assert (bias_over_scale is None and sinks is None) or tc, "score bias and sink ride on the tensor-core decode kernel only"
+    if tc and sinks is not None:
+        rc = lib.llmss_attn_decode_tc_sink(_ptr(q_view), q_view.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                                           block_tables.shape[1], _ptr(seq_lens), _ptr(out_view), out_view.stride(0),
+                                           _ptr(scratch), B, hq, hkv, d, bs, k_cache.shape[0], float(scale), num_splits,
+                                           _DT[q_view.dtype], _ptr(bias_over_scale),
+                                           bias_over_scale.shape[1] if bias_over_scale is not None else 0, _ptr(sinks), _stream())
+        _lib.check(rc, "llmss_attn_decode_tc_sink")
+        _count(1 if num_splits == 1 else 2)
+        return
     if tc and bias_over_scale is not None:
         rc = lib.llmss_attn_decode_tc_bias(_ptr(q_view), q_view.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
                                            block_tables.shape[1], _ptr(seq_lens), _ptr(out_view), out_view.stride(0),
@@ -505,6 +516,16 @@ def latent_decode_splits(B: int, heads: int, max_kv: int) -> int:
     return int(max(1, min(32, 296 // max(1, ctas), max_kv // 256)))
 
 
+def _latent_decode_groups(heads: int, rank: int, block_size: int):
+    """Head ranges of one tensor-core decode call each: all heads at once where the kernel's query tile holds them, else
+    groups of eight (every group reads the latent pages again, which is still far cheaper than the generic kernel)."""
+    if not use_tc_decode(heads, 1, rank, block_size) or _lib.load().llmss_attn_decode_tc_supported(heads, 1, rank, block_size):
+        return [(0, heads)]
+    if not _lib.load().llmss_attn_decode_tc_supported(8, 1, rank, block_size):
+        return None
+    return [(h, min(8, heads - h)) for h in range(0, heads, 8)]
+
+
 def latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype):
     lib = _lib.load()
     T = q_abs.shape[0]
@@ -514,8 +535,10 @@ def latent_attention(q_abs, cache, batch, heads, rank, scale, out_dtype):
     if latent_uses_tc(dt, rank, bs, heads) and q_abs.dtype == dt and out_dtype == dt:
         kv = cache.view(cache.shape[0], 1, bs, rank)       # one shared "KV head" that is key and value at once
         if batch.is_decode:
-            splits = batch.decode_splits or decode_splits(batch.num_seqs, heads, 1, rank, batch.max_kv, dt, bs)
-            attn_decode(q_abs, kv, kv, batch.block_tables, batch.seq_lens, out, heads, 1, rank, scale, splits)
+            for h0, n in _latent_decode_groups(heads, rank, bs):
+                qv, ov = q_abs[:, h0 * rank:(h0 + n) * rank], out[:, h0 * rank:(h0 + n) * rank]
+                splits = batch.decode_splits or decode_splits(batch.num_seqs, n, 1, rank, batch.max_kv, dt, bs)
+                attn_decode(qv, kv, kv, batch.block_tables, batch.seq_lens, ov, n, 1, rank, scale, splits)
             return out
         if _lib.has("llmss_attn_prefill_paged"):
             attn_prefill_paged(q_abs, kv, kv, batch.block_tables, batch.seq_lens, out, batch.cu_q, batch.num_seqs, batch.max_q,
@@ -538,9 +561,9 @@ def latent_uses_tc(dtype, rank: int, block_size: int, heads: int) -> bool:
     """Whether latent_attention() will run on the tcgen05 multi-query kernels (then it wants 16-bit absorbed queries)."""
     if not (_LATENT_TC and dtype != torch.float32 and rank in (64, 128, 256) and block_size in (16, 32, 64) and heads <= 128):
         return False
-    # all heads form one query group over the single latent "KV head": the decode kernel must be able to hold that tile
-    return not use_tc_decode(heads, 1, rank, block_size) or bool(
-        _lib.load().llmss_attn_decode_tc_supported(heads, 1, rank, block_size))
+    # all heads form one query group over the single latent "KV head": the decode kernel must be able to hold that tile,
+    # at once or in groups of eight heads
+    return _latent_decode_groups(heads, rank, block_size) is not None
 
 
 # --------------------------------------------------------------------------- routed experts
@@ -864,8 +887,24 @@ def attention_bias(q, k_cache, v_cache, batch, hq, hkv, dk, dv, scale, dist_bias
     assert k_cache.dtype == dt and (out_dtype or dt) == dt and q.stride(1) == 1
     out = torch.empty(T, hq * dv, dtype=dt, device=q.device)
     if sinks is not None:
-        # a sink logit per head in the softmax denominator: the generic kernel (any sizes, 32-bit scores, softmax and accumulation)
         assert sinks.dtype == torch.float32 and sinks.numel() == hq
+        bs = k_cache.shape[2]
+        if (dist_bias is None and not window and slopes is None and gate is None and _lib.has("llmss_attn_prefill_paged_sink")
+                and attention_bias_uses_tc(dt, dk, dv, bs, scale) and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0):
+            # 16-bit pages of a tensor-core size: the sink joins the final normalisation of the tcgen05 kernels
+            if (batch.is_decode and _lib.has("llmss_attn_decode_tc_sink") and use_tc_decode(hq, hkv, dk, bs)
+                    and lib.llmss_attn_decode_tc_supported(hq, hkv, dk, bs)):
+                splits = batch.decode_splits or decode_splits(batch.num_seqs, hq, hkv, dk, batch.max_kv, dt, bs)
+                attn_decode(q, k_cache, v_cache, batch.block_tables, batch.seq_lens, out, hq, hkv, dk, scale, splits, sinks=sinks)
+                return out
+            rc = lib.llmss_attn_prefill_paged_sink(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
+                                                   batch.block_tables.shape[1], _ptr(batch.seq_lens), _ptr(out), out.stride(0),
+                                                   _ptr(batch.cu_q), batch.num_seqs, max(1, batch.max_q), T, hq, hkv, dk, bs,
+                                                   k_cache.shape[0], float(scale), _DT[dt], None, 0, None, 0, _ptr(sinks), _stream())
+            _lib.check(rc, "llmss_attn_prefill_paged_sink")
+            _count()
+            return out
+        # everything else: the generic kernel (any sizes, true 32-bit; 32-bit scores, softmax and accumulation)
         rc = lib.llmss_attention_sink(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables),
                                       batch.block_tables.shape[1], k_cache.shape[2], _ptr(batch.seq_lens), _ptr(batch.cu_q),
                                       _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0, _ptr(slopes),

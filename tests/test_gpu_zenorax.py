@@ -27,11 +27,16 @@ cases.CONFIGS["wide"] = zenorax_config(128, 211, [
 
 
 def spread_router(t):
-    """16-bit runs: router logits far apart, so that rounding does not flip a choice (a flip moves a position by a whole
-    expert's output and, through the recurrent states, every later one)."""
+    """16-bit runs: choice scores far apart, so that rounding does not flip a choice (a flip moves a position by a whole
+    expert's output and, through the recurrent states, every later one).  Sigmoid scores saturate, so larger router
+    logits would bring them closer; instead the logits shrink and the corrections are spaced widely, in a shuffled order."""
     for k in list(t):
         if k.endswith(".mlp.router"):
-            t[k] = (t[k].float() * 4.0).to(t[k].dtype)
+            t[k] = (t[k].float() * 0.3).to(t[k].dtype)
+        if k.endswith(".mlp.correction"):
+            n = t[k].numel()
+            order = torch.randperm(n, generator=torch.Generator().manual_seed(n))
+            t[k] = (0.5 * order.float() - 0.25 * n).to(t[k].dtype)
 
 
 def test_loaded_library_is_the_in_tree_one():
