@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(NW * 32) attention_bias_kernel(AbArgs a) {
   }
   if (!active) return;
   float gsc = 1.f / l;
-  if (a.sinks != nullptr) {       // the sink has no key and no value: it only enlarges the denominator
+  if (a.sinks != nullptr) {       // the sink is a logit only: it enlarges the denominator and adds nothing to the numerator
     const float sk = a.sinks[h];
     const float mn = fmaxf(m, sk);
     const float corr = expf(m - mn);

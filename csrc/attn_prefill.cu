@@ -85,7 +85,7 @@ struct PArgs {
   int n_dist;
   const float* gate;
   int64_t ldg;
-  // and an attention sink per head: 2^(sinks[h] * log2 e) joins every denominator of head h (no key, no value, not scaled)
+  // and an attention sink per head: 2^(sinks[h] * log2 e) joins every denominator of head h (a bare logit: the score scale does not apply)
   const float* sinks;
 };
 

@@ -2,7 +2,7 @@
 //
 //   rope_norm_kv_write : grouped-query attention whose values are the projected keys.  q and k are rotated (pairs (2i, 2i+1) or
 //                        (i, i + n)), optionally every head is divided by its root mean square, the prepared keys go to the K
-//                        pages, the keys as projected to the V pages, the queries out in the compute type.
+//                        pages, the raw key projection to the V pages, the queries out in the compute type.
 //   latent_rope_prep   : latent attention with a rotated key part, first stage: RMS norm of the query latent (-> GEMM operand),
 //                        RMS norm of the key / value latent and rotation of the shared key part (-> one cache row), sigmoid of
 //                        the gate columns.

@@ -373,6 +373,18 @@ int llmss_attention_sink(const void* q, int64_t ldq, const void* k_cache, const 
                          int max_blocks, int block_size, const int* seq_lens, const int* cu_q, const float* bias, int n_dist,
                          const float* slopes, int window, const float* gate, int64_t ldg, const float* sinks, void* out, int B,
                          int max_q, int hq, int hkv, int dk, int dv, float scale, int dtype, llmss_stream_t stream);
+/* the tcgen05 kernels with a sink logit per q head (sinks [hq] 32-bit; bias_over_scale and gate may be null; scale > 0) */
+int llmss_attn_prefill_paged_sink(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                                  int max_blocks, const int* seq_lens, void* out, int64_t ldo, const int* cu_q, int num_seqs,
+                                  int max_q, int total_q, int hq, int hkv, int d, int block_size, int num_blocks, float scale,
+                                  int dtype, const float* bias_over_scale, int n_dist, const float* gate, int64_t ldg,
+                                  const float* sinks, llmss_stream_t stream);
+int llmss_attn_decode_tc_sink(const void* q, int64_t ldq, const void* k_cache, const void* v_cache, const int* block_tables,
+                              int max_blocks, const int* seq_lens, void* out, int64_t ldo, float* scratch, int B, int hq, int hkv,
+                              int d, int block_size, int num_blocks, float scale, int num_splits, int dtype,
+                              const float* bias_over_scale, int n_dist, const float* sinks, llmss_stream_t stream);
+int llmss_attn_decode_combine_sink(const float* part_o, const float* part_ml, void* out, int64_t ldo, int B, int hq, int d,
+                                   int num_splits, int dtype, const float* sinks, llmss_stream_t stream);
 /* llmss_moe_route with score_kind (0 softmax, 1 sigmoid), a per-expert correction added for the choice only (or null), groups
  * scored by the sum of their group_top best, weights renormalised over the chosen experts or not */
 int llmss_moe_route_ex(const float* z, int64_t ldz, int T, int E, int top, int groups, int keep, float route_scale, int score_kind,

@@ -373,7 +373,7 @@ class WindowAttention:
 
 
 class SinkAttention:
-    """Grouped-query softmax attention whose values are the keys as projected (there is no value projection), with an
+    """Grouped-query softmax attention in which the raw key projection doubles as the value (no W_v), with an
     attention sink.
 
         q, k = W h ;  v = k                                          (v: before rotation and norm)

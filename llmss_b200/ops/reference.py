@@ -256,7 +256,7 @@ def moe_route(z, experts: int, top: int, groups: int, keep: int, route_scale: fl
     Scores s = softmax(z) or sigmoid(z) (``score``); experts are *chosen* by s + correction (``correction`` [experts], or
     none) while the weights are the chosen experts' s.  A group of neighbouring experts scores as the sum of its
     ``group_top`` largest choice scores (1: its best expert); only experts of the best ``keep`` groups are eligible (the
-    others count as minus infinity: choice scores may be negative).  ``renorm``: weights / (their sum + 1e-20); both forms
+    rest is masked with -inf, not 0, because a choice score may be below 0).  ``renorm``: weights / (their sum + 1e-20); both forms
     times ``route_scale``.  Ties go to the lower index (stable sort), like the CUDA kernel."""
     zf = z.float()
     s = torch.softmax(zf, dim=-1) if score == "softmax" else torch.sigmoid(zf)
@@ -615,8 +615,10 @@ def attention_bias(q, k_cache, v_cache, block_tables, seq_lens, cu_q, hq: int, h
                    dist_bias, gate=None, out_dtype=None, window: int = 0, slopes=None, sinks=None):
     """Causal softmax attention over the paged cache with key size dk, value size dv, grouped heads, an additive bias
     dist_bias[h, min(i - j, last)] per head and distance (or none), a linear penalty slopes[h] * (i - j) taken off the
-    scores (or none), a sliding window (``window`` > 0: query i sees keys j with 0 <= i - j < window), and an optional
-    per-head output gate sigmoid(gate[t, h])."""
+    scores (or none), a sliding window (``window`` > 0: query i sees keys j with 0 <= i - j < window), an optional
+    per-head output gate sigmoid(gate[t, h]), and an optional attention sink: ``sinks`` [hq] is a bare logit per head whose
+    exponential is one more term of every softmax denominator of that head (nothing is added to the numerator, and the
+    score scale does not apply to it)."""
     T = q.shape[0]
     bs, g = k_cache.shape[2], hq // hkv
     out = torch.zeros(T, hq, dv, dtype=torch.float32, device=q.device)
@@ -831,7 +833,7 @@ def _rotate_by_table(x, positions, freq, mag: float, interleaved: bool):
 
 def rope_norm_kv_write(qk, hq: int, hkv: int, d: int, freq, mag: float, interleaved: bool, unit_norm: bool, eps: float,
                        positions, slot_mapping, k_cache, v_cache, out_dtype=None):
-    """Queries and keys of grouped-query attention whose values are the keys as projected.  qk [T, hq*d + hkv*d] 32-bit.
+    """Queries and keys of grouped-query attention in which the raw key projection doubles as the value.  qk [T, hq*d + hkv*d] 32-bit.
     q and k are rotated by the frequency table (pairs (2i, 2i+1) if ``interleaved`` else (i, i + n)), then -- ``unit_norm``
     -- every head is divided by its root mean square (no weight).  The prepared keys go to the K pages, the projected
     keys themselves (before rotation and norm) to the V pages.  Returns the queries [T, hq * d]."""

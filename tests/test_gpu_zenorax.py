@@ -124,6 +124,20 @@ def test_schedules_in_16_bit_agree_with_each_other(tmp_path):
         assert (d < 8e-2).float().mean() >= 0.95, (sizes, d)
 
 
+def test_latent_row_of_256_with_sixteen_heads(tmp_path):
+    """bfloat16: a latent row of 192 + 64 numbers and 16 heads -- the tensor-core paged kernel for portions, the tensor-core
+    decode kernel in two groups of eight heads for single tokens -- against the oracle."""
+    cfg = zenorax_config(128, 211, [cases.lat(heads=16, dim=32, rot_dim=64, vdim=16, kv_rank=192, q_rank=64, scale=0.25),
+                                    cases.att(heads=8, kv_heads=2, dim=64, scale=0.3)], taps=2, embed_scale=11.0)
+    cfg, W, eng = cases.build(tmp_path, cfg, "cuda", BF16)
+    toks = cases.tokens_for(cfg, 200, 5)
+    want = cases.want_logits(toks, cfg, W)
+    for sizes in ([200], [150, 1], [70, 3, 64, 1]):
+        got = cases.feed_in_portions(eng, "p", toks, sizes).double().cpu()
+        d = (got - want).abs().max(-1).values / want.std()
+        assert d.max() < 8e-2, (sizes, d)
+
+
 @pytest.mark.parametrize("graph", [False, True])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_generation(tmp_path, dtype, graph):

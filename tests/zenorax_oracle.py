@@ -88,7 +88,7 @@ def sink_attention(h, positions, p, pre, m, eps):
     H, G, d = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
     q = (h @ p[pre + "q"].T).view(T, H, d)
     k = (h @ p[pre + "k"].T).view(T, G, d)
-    v = k                                                                       # the values are the keys as projected
+    v = k                                                                       # no value projection: the raw keys serve
     q = rms_div(rotate(q, positions, m["rot"], False), eps)
     kn = rms_div(rotate(k, positions, m["rot"], False), eps)
     rep = H // G
