@@ -15,20 +15,24 @@
 //
 // Every rotation takes its frequencies as a 64-bit table [n] (n pairs: the first 2 n channels rotate, the rest pass) and a
 // magnitude that multiplies cos and sin, so linear interpolation, YaRN or any other schedule is a different table.  The angle
-// position * frequency, its cosine and its sine are formed in 64-bit once per token and pair.  Everything else is 32-bit.
+// position * frequency is formed and reduced to [-pi, pi] in 64-bit once per token and pair.  Everything else is 32-bit.
 #include "common.cuh"
 
 namespace {
 
 constexpr int kMaxPairs = 256;      // rotated pairs per head (512 rotated channels)
 
-// cos / sin of this token's angles into shared memory (threads 0 .. n - 1)
+// cos / sin of this token's angles into shared memory.  The angle position * frequency and its reduction to [-pi, pi] are
+// 64-bit (one multiply, one rounding, one fused multiply-add); cosine and sine of the reduced angle are 32-bit.
 __device__ __forceinline__ void token_angles(const double* __restrict__ freq, int n, int pos, float mag, float* cs, float* sn) {
+  constexpr double kTwoPi = 6.283185307179586476925286766559;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    double s, c;
-    sincos((double)pos * freq[i], &s, &c);
-    cs[i] = (float)(c * (double)mag);
-    sn[i] = (float)(s * (double)mag);
+    const double a = (double)pos * freq[i];
+    const float r = (float)fma(-rint(a * (1.0 / kTwoPi)), kTwoPi, a);
+    float s, c;
+    sincosf(r, &s, &c);
+    cs[i] = c * mag;
+    sn[i] = s * mag;
   }
 }
 
@@ -42,21 +46,65 @@ __device__ __forceinline__ float rotated(const float* __restrict__ x, int c, int
   return c < n ? fmaf(x[c], cs[c], -x[c + n] * sn[c]) : fmaf(x[c], cs[c - n], x[c - n] * sn[c - n]);
 }
 
-// grid T, block 256; warps walk the hq + hkv heads of the token
-template <typename T>
+// grid T, block 256; the token's row is staged in shared memory (16-byte loads where the row allows), then the warps walk
+// its hq + hkv heads.  STAGE = false: rows too long for shared memory are read in place.
+template <typename T, bool STAGE>
 __global__ void __launch_bounds__(256) rope_norm_kv_write_kernel(const float* __restrict__ qk, int64_t ld, int hq, int hkv, int d,
                                                                  const double* __restrict__ freq, int n, float mag, int interleaved,
                                                                  int unit_norm, float eps, const int* __restrict__ positions,
                                                                  const int* __restrict__ slots, T* __restrict__ k_cache,
                                                                  T* __restrict__ v_cache, int bs, T* __restrict__ q_out) {
   __shared__ float cs[kMaxPairs], sn[kMaxPairs];
+  extern __shared__ __align__(16) float rowbuf[];
   const int64_t t = blockIdx.x;
   token_angles(freq, n, positions[t], mag, cs, sn);
+  const float* src = qk + t * ld;
+  if constexpr (STAGE) {
+    const int cols = (hq + hkv) * d;
+    if ((cols & 3) == 0 && (ld & 3) == 0 && (((uintptr_t)qk) & 15) == 0) {
+      for (int c = threadIdx.x * 4; c < cols; c += 1024) *reinterpret_cast<float4*>(rowbuf + c) = *reinterpret_cast<const float4*>(src + c);
+    } else {
+      for (int c = threadIdx.x; c < cols; c += 256) rowbuf[c] = src[c];
+    }
+    src = rowbuf;
+  }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = slots[t];
+  if constexpr (STAGE) {
+    // A lane owns whole pairs: it rotates them in place in the staged row (one pass, both outputs of a pair at once) and sums
+    // the squares; the second pass scales and stores in channel order.  The projected keys leave for the V pages first.
+    for (int hh = warp; hh < hq + hkv; hh += 8) {
+      float* x = rowbuf + (int64_t)hh * d;
+      const bool is_k = hh >= hq;
+      const int64_t base = is_k && slot >= 0 ? (((int64_t)(slot / bs) * hkv + (hh - hq)) * bs + slot % bs) * d : 0;
+      if (is_k && slot >= 0)
+        for (int c = lane; c < d; c += 32) v_cache[base + c] = from_f32<T>(x[c]);
+      __syncwarp();
+      float ss = 0.f;
+      for (int i = lane; i < n; i += 32) {
+        const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + n;
+        const float u = x[iu], v = x[iv], c = cs[i], sgn = sn[i];
+        const float ou = fmaf(u, c, -v * sgn), ov = fmaf(v, c, u * sgn);
+        x[iu] = ou;
+        x[iv] = ov;
+        ss = fmaf(ou, ou, fmaf(ov, ov, ss));
+      }
+      if (unit_norm)
+        for (int c = 2 * n + lane; c < d; c += 32) ss = fmaf(x[c], x[c], ss);
+      const float rstd = unit_norm ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+      __syncwarp();
+      if (!is_k) {
+        T* o = q_out + t * (int64_t)hq * d + (int64_t)hh * d;
+        for (int c = lane; c < d; c += 32) o[c] = from_f32<T>(x[c] * rstd);
+      } else if (slot >= 0) {
+        for (int c = lane; c < d; c += 32) k_cache[base + c] = from_f32<T>(x[c] * rstd);
+      }
+    }
+    return;
+  }
   for (int hh = warp; hh < hq + hkv; hh += 8) {
-    const float* x = qk + t * ld + (int64_t)hh * d;
+    const float* x = src + (int64_t)hh * d;
     float rstd = 1.f;
     if (unit_norm) {
       float ss = 0.f;
@@ -176,7 +224,7 @@ struct SwArgs {
   int W; float eps;
 };
 
-constexpr int kSwRegs = 8;             // columns kept in registers per thread and pass: W <= 256 * VEC * kSwRegs, else re-read
+constexpr int kSwRegs = 4;             // columns kept in registers per thread and pass: W <= 256 * VEC * kSwRegs, else re-read
 
 template <int VEC> __device__ __forceinline__ void ldv(const float* p, float (&v)[VEC]) {
   if constexpr (VEC == 4) {
@@ -233,7 +281,7 @@ __device__ __forceinline__ void sandwich_emit(const SwArgs& a, int64_t t, int c,
 }
 
 template <typename TO, int VEC>
-__global__ void __launch_bounds__(256) sandwich_residual_kernel(SwArgs a) {
+__global__ void __launch_bounds__(256, 5) sandwich_residual_kernel(SwArgs a) {
   __shared__ float red[8];
   const int64_t t = blockIdx.x;
   const int W = a.W;
@@ -299,9 +347,16 @@ LLMSS_API int llmss_rope_norm_kv_write(const float* qk, int64_t ld, int hq, int 
   LLMSS_REQUIRE(n_pairs >= 0 && n_pairs <= kMaxPairs && 2 * n_pairs <= d, "rope_norm_kv_write: %d rotated pairs for head size %d (at most %d)",
                 n_pairs, d, kMaxPairs);
   if (T_ <= 0) return 0;
-  LLMSS_BY_DTYPE(dtype, (rope_norm_kv_write_kernel<T><<<T_, 256, 0, stream>>>(qk, ld, hq, hkv, d, freq, n_pairs, mag, interleaved, unit_norm,
-                                                                             eps, positions, slots, (T*)k_cache, (T*)v_cache, block_size,
-                                                                             (T*)q_out)));
+  const size_t row_bytes = sizeof(float) * (size_t)(hq + hkv) * d;
+  if (row_bytes <= 40 * 1024) {      // within the default dynamic shared memory: the row is staged
+    LLMSS_BY_DTYPE(dtype, (rope_norm_kv_write_kernel<T, true><<<T_, 256, row_bytes, stream>>>(
+                              qk, ld, hq, hkv, d, freq, n_pairs, mag, interleaved, unit_norm, eps, positions, slots, (T*)k_cache,
+                              (T*)v_cache, block_size, (T*)q_out)));
+  } else {
+    LLMSS_BY_DTYPE(dtype, (rope_norm_kv_write_kernel<T, false><<<T_, 256, 0, stream>>>(
+                              qk, ld, hq, hkv, d, freq, n_pairs, mag, interleaved, unit_norm, eps, positions, slots, (T*)k_cache,
+                              (T*)v_cache, block_size, (T*)q_out)));
+  }
   LLMSS_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -47,7 +47,8 @@ def test_loaded_library_is_the_in_tree_one():
 
 
 @pytest.mark.parametrize("hq,hkv,d,dims,inter", [(4, 2, 12, 8, False), (1, 1, 20, 20, False), (6, 6, 8, 2, True), (12, 3, 40, 24, False),
-                                                 (2, 1, 64, 64, True), (32, 8, 128, 128, False), (9, 9, 300, 100, False)])
+                                                 (2, 1, 64, 64, True), (32, 8, 128, 128, False), (9, 9, 300, 100, False), (80, 16, 128, 64, True),
+                                                 (5, 5, 33, 6, False)])
 def test_rotation_and_pages(hq, hkv, d, dims, inter):
     cases.test_rotation_unit_norm_and_pages(hq, hkv, d, dims, inter, "cuda", F32, 1e-5)
     cases.test_rotation_unit_norm_and_pages(hq, hkv, d, dims, inter, "cuda", BF16, 2e-2)
