@@ -106,6 +106,7 @@ class RotaryLatentAttention:
         self.c_off = base + self.q_rank
         self.g_off = self.c_off + self.rank + self.rot
         self.w_dq = self.w_dkv = self.w_g = None
+        self.freq = self.freq.to(torch.float64).to(self.w_o.device).contiguous()     # the kernels read the table on the device
         H, d, R = self.heads, self.dim, self.rank
         # [(head, dim), rank] -> [(head, rank), dim]: the absorption contracts over dim (see LatentAttention.bind)
         self.w_uk = self.w_uk.view(H, d, R).transpose(1, 2).contiguous().view(H * R, d)

@@ -406,6 +406,7 @@ class SinkAttention:
     def set_weights(self, wq, wk, sinks, w_o):
         self.w_in = torch.cat([wq, wk], dim=0).contiguous()
         self.sinks, self.w_o = sinks, w_o.contiguous()
+        self.freq = self.freq.to(torch.float64).to(w_o.device).contiguous()     # the kernels read the table on the device
 
     def forward(self, h, batch, lc, dtype):
         H, G, D = self.heads, self.kv_heads, self.dim

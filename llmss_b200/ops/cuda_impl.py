@@ -969,7 +969,10 @@ _FREQ_DEV = {}
 
 
 def _freq_dev(freq, device):
-    """The 64-bit frequency table on the device, kept per (table, device) for the life of the process (a captured graph points at it)."""
+    """The 64-bit frequency table on the device: the caller's own tensor if it lives there (a layer keeps its table), else a copy
+    kept per (table, device) for the life of the process (a captured graph points at it)."""
+    if freq.is_cuda and freq.dtype == torch.float64 and freq.is_contiguous():
+        return freq
     key = (tuple(freq.tolist()), str(device))
     t = _FREQ_DEV.get(key)
     if t is None:

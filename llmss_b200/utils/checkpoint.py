@@ -359,7 +359,7 @@ PRESETS.update({
 })
 
 
-def zenorax_config(width: int, vocab: int, layers, taps: int = 3, embed_scale: float = 1.0, softcap: float = 30.0,
+def zenorax_config(width: int, vocab: int, layers, taps: int = 4, embed_scale: float = 1.0, softcap: float = 25.0,
                    eps: float = 1e-6) -> dict:
     """config.json of a Zenorax model.  ``layers``: one dict per layer,
     {"type": "latent_attention", heads, dim, rot_dim, vdim, kv_rank, q_rank, optionally scale, base, scaling} |
@@ -445,7 +445,7 @@ def _zenorax_preset(width, vocab, heads, n_blocks, experts=16, top=4, groups=4, 
     row is 192 + 64 = 256 numbers, a size the tensor-core multi-query kernels take."""
     mlp = dict(experts=experts, top=top, groups=groups, keep=keep, ff=eff)
     lat = dict(type="latent_attention", heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=192, q_rank=width // 2,
-               scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}, mlp=mlp)
+               scaling={"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}, mlp=mlp)
     att = dict(type="attention", heads=heads, kv_heads=max(1, heads // 4), dim=128, scaling={"factor": 2.0}, mlp=mlp)
     rec = dict(type="hgrn2", heads=heads, dim=128, vdim=128, mlp=mlp)
     return zenorax_config(width, vocab, [dict(L) for _ in range(n_blocks) for L in (lat, att, rec)], taps=4, embed_scale=width ** 0.5)

@@ -71,7 +71,7 @@ def test_row_kernels():
     cases.test_soft_cap("cuda")
 
 
-@pytest.mark.parametrize("E,top,groups,keep", [(8, 4, 2, 1), (6, 2, 3, 2), (4, 1, 4, 4), (16, 4, 4, 2), (64, 6, 8, 3), (5, 2, 5, 3), (12, 3, 1, 1),
+@pytest.mark.parametrize("E,top,groups,keep", [(8, 3, 2, 1), (6, 2, 3, 2), (4, 1, 4, 4), (16, 4, 4, 2), (64, 6, 8, 3), (5, 2, 5, 3), (12, 3, 1, 1),
                                                (256, 8, 8, 4), (160, 6, 40, 7)])
 def test_router(E, top, groups, keep):
     cases.test_sigmoid_router_with_correction(E, top, groups, keep, "cuda")
