@@ -83,7 +83,7 @@ def test_gated_recurrence(H, D, Dv):
 
 
 @pytest.mark.parametrize("dtype,tol", MODES)
-@pytest.mark.parametrize("name", ["latent", "attention", "hgrn2", "experts", "mixed", "edges", "wide"])
+@pytest.mark.parametrize("name", ["latent", "attention", "hgrn2", "experts", "mixed", "edges", "odd", "wide"])
 def test_whole_prompt_and_residual_stream(tmp_path, name, dtype, tol):
     if dtype == BF16:
         cfg, W, eng = cases.build(tmp_path, name, "cuda", dtype, tweak=spread_router)
@@ -96,7 +96,7 @@ def test_whole_prompt_and_residual_stream(tmp_path, name, dtype, tol):
         cases.test_whole_prompt_and_residual_stream(tmp_path, name, "cuda", dtype, tol)
 
 
-@pytest.mark.parametrize("name", ["mixed", "edges", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "edges", "odd", "wide"])
 def test_decode_and_portions(tmp_path, name):
     cases.test_decode_token_by_token_and_portions(tmp_path, name, "cuda", F32, 3e-4)
 

@@ -65,6 +65,11 @@ CONFIGS = {
         att(heads=5, kv_heads=5, dim=6, rot_dims=2, mlp=dict(experts=5, top=2, groups=5, keep=3, ff=8)),
         lat(heads=5, dim=4, rot_dim=2, vdim=4, kv_rank=30, q_rank=6, scaling={"factor": 1.0, "original": 8, "fast": 4.0, "slow": 1.0})],
         taps=1, embed_scale=1.0, softcap=0.0),
+    # nothing a multiple of 4: the scalar forms of the row kernels, matrix products off the 16-byte rules, five taps
+    "odd": zenorax_config(50, 101, [
+        lat(heads=3, dim=5, rot_dim=6, vdim=7, kv_rank=9, q_rank=7, mlp=dict(experts=3, top=2, groups=1, keep=1, ff=9)),
+        att(heads=3, kv_heads=1, dim=9, rot_dims=6, mlp=dict(experts=9, top=2, groups=3, keep=1, ff=5)),
+        rec(heads=5, dim=3, vdim=7)], taps=5, embed_scale=7.0, softcap=9.0),
 }
 
 
