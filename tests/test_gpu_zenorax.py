@@ -125,6 +125,26 @@ def test_schedules_in_16_bit_agree_with_each_other(tmp_path):
         assert (d < 8e-2).float().mean() >= 0.95, (sizes, d)
 
 
+def test_decode_batch_of_unequal_requests_in_16_bit(tmp_path):
+    """bfloat16: three requests of different lengths decode together (the tensor-core decode kernels with the sink and over the
+    latent rows, several sequences per launch); every request equals itself fed whole."""
+    cfg, W, eng = cases.build(tmp_path, "wide", "cuda", BF16, tweak=spread_router)
+    reqs = {k: cases.tokens_for(cfg, n, 20 + i) for i, (k, n) in enumerate([("a", 90), ("b", 171), ("c", 40)])}
+    whole = {k: cases.feed_in_portions(eng, "w" + k, t, [len(t)]).double().cpu() for k, t in reqs.items()}
+    std = max(v.std().item() for v in whole.values())
+    tail = 12
+    out = eng.feed([(k, t[:-tail], [len(t) - tail - 1]) for k, t in reqs.items()])
+    got = {k: [out[i:i + 1]] for i, k in enumerate(reqs)}
+    for j in range(tail):
+        last = j == tail - 1
+        out = eng.feed([(k, [t[len(t) - tail + j]], [0]) for k, t in reqs.items()], list(reqs) if last else [])
+        for i, k in enumerate(reqs):
+            got[k].append(out[i:i + 1])
+    for k, t in reqs.items():
+        d = (torch.cat(got[k]).double().cpu() - whole[k][len(t) - tail - 1:]).abs().max(-1).values / std
+        assert d.max() < 8e-2, (k, d)
+
+
 def test_latent_row_of_256_with_sixteen_heads(tmp_path):
     """bfloat16: a latent row of 192 + 64 numbers and 16 heads -- the tensor-core paged kernel for portions, the tensor-core
     decode kernel in two groups of eight heads for single tokens -- against the oracle."""
