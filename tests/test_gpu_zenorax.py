@@ -18,7 +18,7 @@ MODES = [pytest.param(F32, 3e-4, id="f32"), pytest.param(BF16, 8e-2, id="bf16")]
 # one of 104 (the generic kernel), key sizes over one and several register strips of the recurrence, many query heads per
 # key/value head, a width that takes the vector forms and fits the tensor-core GEMM's 16-byte rules
 cases.CONFIGS["wide"] = zenorax_config(128, 211, [
-    cases.lat(heads=8, dim=32, rot_dim=16, vdim=24, kv_rank=48, q_rank=40, mlp=dict(experts=8, top=2, groups=4, keep=2, ff=64)),
+    cases.lat(heads=8, dim=24, rot_dim=16, vdim=24, kv_rank=48, q_rank=40, mlp=dict(experts=8, top=2, groups=4, keep=2, ff=64)),
     cases.att(heads=12, kv_heads=1, dim=40, rot_dims=24, mlp=dict(experts=16, top=4, groups=4, keep=2, ff=32)),
     cases.rec(heads=2, dim=136, vdim=24),
     cases.lat(heads=3, dim=16, rot_dim=8, vdim=40, kv_rank=96, q_rank=64),
